@@ -1,0 +1,73 @@
+"""ctypes binding of libdsa_b200.so -- the only way the package reaches the GPU.
+
+There is no fallback: if the shared library is missing or lacks a symbol declared in
+include/dsa_b200.h, importing an operator raises.  Build it with
+`python -m auto_gpu_kernel_b200.build` (nvcc, sm_100a).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+from . import build as _build
+
+_c_int = ctypes.c_int
+_c_i64 = ctypes.c_int64
+_c_size = ctypes.c_size_t
+_ptr = ctypes.c_void_p
+_c_float = ctypes.c_float
+
+# name -> (restype, argtypes); mirrors include/dsa_b200.h one to one.
+SIGNATURES = {
+    "dsa_b200_version": (_c_int, []),
+    "dsa_b200_error_string": (ctypes.c_char_p, [_c_int]),
+    "dsa_indexer_workspace_bytes": (_c_size, [_c_int, _c_int]),
+    "dsa_indexer_topk": (_c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr, _c_i64, _c_int,
+                                  _c_int, _c_int, _ptr, _c_size, _ptr, _ptr]),
+    "dsa_indexer_scores": (_c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr, _c_i64, _c_int,
+                                    _c_int, _c_int, _c_int, _ptr, _ptr]),
+    "dsa_topk_select": (_c_int, [_ptr, _c_i64, _ptr, _ptr, _c_i64, _ptr, _c_i64, _c_int, _c_int,
+                                 _ptr, _ptr]),
+    "dsa_sparse_attn_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int]),
+    "dsa_sparse_attn": (_c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _c_float, _ptr, _ptr,
+                                 _c_int, _c_int, _c_int, _c_i64, _ptr, _c_size, _ptr, _ptr]),
+}
+
+_lib = None
+
+
+def library_path() -> Path:
+    override = os.environ.get("DSA_B200_LIB")
+    return Path(override) if override else _build.PKG_DIR / _build.LIB_NAME
+
+
+def load(build_if_missing: bool = True):
+    """Load (building first when the sources are newer) and type the C ABI.  Raises on failure."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path()
+    if build_if_missing and "DSA_B200_LIB" not in os.environ and _build.needs_build(path):
+        _build.build(path)
+    if not path.exists():
+        raise RuntimeError(f"{path} is missing: run `python -m auto_gpu_kernel_b200.build`")
+    lib = ctypes.CDLL(str(path))
+    for name, (res, args) in SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as exc:
+            raise RuntimeError(f"{path} does not export {name}") from exc
+        fn.restype = res
+        fn.argtypes = args
+    if lib.dsa_b200_version() != 1:
+        raise RuntimeError(f"{path}: ABI version {lib.dsa_b200_version()} != 1")
+    _lib = lib
+    return lib
+
+
+def check(code: int, what: str):
+    """Turn a non-zero return code of the C ABI into a RuntimeError."""
+    if code != 0:
+        text = load().dsa_b200_error_string(code).decode()
+        raise RuntimeError(f"{what}: {text} (code {code})")

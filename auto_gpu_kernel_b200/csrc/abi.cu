@@ -1,0 +1,150 @@
+// extern "C" boundary of libdsa_b200.so: argument checks on the host, then kernel launches on the
+// caller's stream.  No allocation, no synchronisation, no exceptions cross this boundary.
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace dsa {
+cudaError_t launch_indexer_score_simt(const void*, const void*, const float*, const int32_t*,
+                                      const int32_t*, int64_t, float*, int64_t, int, int, int,
+                                      int32_t*, cudaStream_t);
+cudaError_t launch_indexer_score_tc(const void*, const void*, const float*, const int32_t*,
+                                    const int32_t*, int64_t, float*, int64_t, int, int, int, int,
+                                    int32_t*, cudaStream_t);
+cudaError_t launch_topk_select(const float*, int64_t, const int32_t*, const int32_t*, int64_t,
+                               int32_t*, int64_t, int, int, int32_t*, cudaStream_t);
+cudaError_t launch_sparse_attn_simt(const void*, const void*, const void*, const void*,
+                                    const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
+                                    int, void*, int32_t*, cudaStream_t);
+int att_pick_splits(int tokens, int topk);
+size_t att_workspace_bytes(int tokens, int splits);
+}  // namespace dsa
+
+namespace {
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline size_t round256(size_t n) { return (n + 255) / 256 * 256; }
+// score rows are padded to a multiple of 128 tokens so a 2-page tile never crosses rows
+inline int64_t score_row_stride(int max_pages) { return ((int64_t)max_pages * dsa::kPage + 127) / 128 * 128; }
+}  // namespace
+
+extern "C" {
+
+int dsa_b200_version(void) { return DSA_B200_ABI_VERSION; }
+
+const char* dsa_b200_error_string(int code) {
+  switch (code) {
+    case DSA_OK: return "ok";
+    case DSA_ERR_NULL_POINTER: return "dsa_b200: null pointer argument";
+    case DSA_ERR_BAD_SHAPE: return "dsa_b200: unsupported or inconsistent shape";
+    case DSA_ERR_WORKSPACE_TOO_SMALL: return "dsa_b200: workspace too small";
+    case DSA_ERR_MISALIGNED: return "dsa_b200: pointer or stride not 16-byte aligned";
+    case DSA_ERR_UNSUPPORTED: return "dsa_b200: variant not available";
+    default: break;
+  }
+  if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+  return "dsa_b200: unknown error code";
+}
+
+size_t dsa_indexer_workspace_bytes(int batch, int max_pages) {
+  if (batch <= 0 || max_pages <= 0) return 256;
+  return round256((size_t)batch * score_row_stride(max_pages) * sizeof(float));
+}
+
+static int scores_impl(const void* q_fp8, const void* k_cache, const float* weights,
+                       const int32_t* seq_lens, const int32_t* block_table,
+                       int64_t block_table_stride, float* scores, int64_t score_stride, int batch,
+                       int num_pages, int max_pages, int variant, int skip_short,
+                       int32_t* status_dev, void* stream) {
+  if (batch == 0) return DSA_OK;
+  if (!q_fp8 || !k_cache || !weights || !seq_lens || !block_table || !scores)
+    return DSA_ERR_NULL_POINTER;
+  if (batch < 0 || batch > 65535 || num_pages <= 0 || max_pages <= 0 || block_table_stride < 0 ||
+      score_stride < (int64_t)max_pages * dsa::kPage)
+    return DSA_ERR_BAD_SHAPE;
+  if (!aligned16(q_fp8) || !aligned16(k_cache) || !aligned16(scores) || (score_stride & 3))
+    return DSA_ERR_MISALIGNED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (variant == 1) {
+    e = dsa::launch_indexer_score_simt(q_fp8, k_cache, weights, seq_lens, block_table,
+                                       block_table_stride, scores, score_stride, batch, num_pages,
+                                       max_pages, status_dev, s);
+  } else if (variant == 0) {
+    e = dsa::launch_indexer_score_tc(q_fp8, k_cache, weights, seq_lens, block_table,
+                                     block_table_stride, scores, score_stride, batch, num_pages,
+                                     max_pages, skip_short, status_dev, s);
+  } else {
+    return DSA_ERR_UNSUPPORTED;
+  }
+  return static_cast<int>(e);
+}
+
+int dsa_indexer_scores(const void* q_fp8, const void* k_cache, const float* weights,
+                       const int32_t* seq_lens, const int32_t* block_table,
+                       int64_t block_table_stride, float* scores, int64_t score_stride, int batch,
+                       int num_pages, int max_pages, int variant, int32_t* status_dev,
+                       void* stream) {
+  return scores_impl(q_fp8, k_cache, weights, seq_lens, block_table, block_table_stride, scores,
+                     score_stride, batch, num_pages, max_pages, variant, 0, status_dev, stream);
+}
+
+int dsa_topk_select(const float* scores, int64_t score_stride, const int32_t* seq_lens,
+                    const int32_t* block_table, int64_t block_table_stride, int32_t* topk_out,
+                    int64_t topk_stride, int batch, int max_pages, int32_t* status_dev,
+                    void* stream) {
+  if (batch == 0) return DSA_OK;
+  if (!scores || !seq_lens || !block_table || !topk_out) return DSA_ERR_NULL_POINTER;
+  if (batch < 0 || max_pages <= 0 || topk_stride < dsa::kTopK || block_table_stride < 0)
+    return DSA_ERR_BAD_SHAPE;
+  return static_cast<int>(dsa::launch_topk_select(scores, score_stride, seq_lens, block_table,
+                                                  block_table_stride, topk_out, topk_stride, batch,
+                                                  max_pages, status_dev,
+                                                  static_cast<cudaStream_t>(stream)));
+}
+
+int dsa_indexer_topk(const void* q_fp8, const void* k_cache, const float* weights,
+                     const int32_t* seq_lens, const int32_t* block_table,
+                     int64_t block_table_stride, int32_t* topk_out, int64_t topk_stride, int batch,
+                     int num_pages, int max_pages, void* workspace, size_t workspace_bytes,
+                     int32_t* status_dev, void* stream) {
+  if (batch == 0) return DSA_OK;
+  if (!workspace) return DSA_ERR_NULL_POINTER;
+  if (workspace_bytes < dsa_indexer_workspace_bytes(batch, max_pages))
+    return DSA_ERR_WORKSPACE_TOO_SMALL;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return DSA_ERR_MISALIGNED;
+  float* scores = static_cast<float*>(workspace);
+  const int64_t stride = score_row_stride(max_pages);
+  // rows of at most 2048 tokens are emitted whole by the selection: their scores are skipped
+  int rc = scores_impl(q_fp8, k_cache, weights, seq_lens, block_table, block_table_stride, scores,
+                       stride, batch, num_pages, max_pages, 0, 1, status_dev, stream);
+  if (rc != DSA_OK) return rc;
+  return dsa_topk_select(scores, stride, seq_lens, block_table, block_table_stride, topk_out,
+                         topk_stride, batch, max_pages, status_dev, stream);
+}
+
+size_t dsa_sparse_attn_workspace_bytes(int tokens, int heads, int topk) {
+  if (tokens <= 0 || heads != dsa::kHeads) return 256;
+  return round256(dsa::att_workspace_bytes(tokens, dsa::att_pick_splits(tokens, topk)));
+}
+
+int dsa_sparse_attn(const void* q_nope, const void* q_pe, const void* ckv, const void* kpe,
+                    const int32_t* sparse_indices, int64_t index_stride, float sm_scale, void* out,
+                    float* lse, int tokens, int heads, int topk, int64_t num_slots, void* workspace,
+                    size_t workspace_bytes, int32_t* status_dev, void* stream) {
+  if (tokens == 0) return DSA_OK;
+  if (!q_nope || !q_pe || !ckv || !kpe || !sparse_indices || !out || !lse || !workspace)
+    return DSA_ERR_NULL_POINTER;
+  if (tokens < 0 || heads != dsa::kHeads || topk <= 0 || num_slots <= 0 || index_stride < topk)
+    return DSA_ERR_BAD_SHAPE;
+  if (!aligned16(q_nope) || !aligned16(q_pe) || !aligned16(ckv) || !aligned16(kpe) ||
+      !aligned16(out) || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+    return DSA_ERR_MISALIGNED;
+  if (workspace_bytes < dsa_sparse_attn_workspace_bytes(tokens, heads, topk))
+    return DSA_ERR_WORKSPACE_TOO_SMALL;
+  const int splits = dsa::att_pick_splits(tokens, topk);
+  return static_cast<int>(dsa::launch_sparse_attn_simt(
+      q_nope, q_pe, ckv, kpe, sparse_indices, index_stride, sm_scale, out, lse, tokens, topk,
+      num_slots, splits, workspace, status_dev, static_cast<cudaStream_t>(stream)));
+}
+
+}  // extern "C"

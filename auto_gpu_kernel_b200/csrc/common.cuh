@@ -1,0 +1,47 @@
+// Shared device/host helpers for the dsa_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/dsa_b200.h"
+
+namespace dsa {
+
+constexpr int kPage = DSA_PAGE_SIZE;
+constexpr int kIdxHeads = DSA_INDEX_HEADS;
+constexpr int kIdxDim = DSA_INDEX_DIM;
+constexpr int kPageBytes = DSA_INDEX_PAGE_BYTES;
+constexpr int kPageDataBytes = kPage * kIdxDim;  // 8192
+constexpr int kTopK = DSA_TOPK;
+constexpr int kHeads = DSA_ATTN_HEADS;
+constexpr int kCkv = DSA_CKV_DIM;
+constexpr int kKpe = DSA_KPE_DIM;
+
+// Upper bound on polls of any device-side wait.  Each poll is a try_wait with a hardware
+// suspend-time hint, so this is far longer than any legitimate wait, yet a lost arrival ends
+// the kernel with DSA_STATUS_WAIT_TIMEOUT instead of hanging the GPU.
+constexpr uint32_t kMaxPolls = 1u << 22;
+
+__device__ __forceinline__ void raise_status(int32_t* status, uint32_t bits) {
+  if (status != nullptr) atomicOr(reinterpret_cast<unsigned int*>(status), bits);
+}
+
+__device__ __forceinline__ float e4m3_to_float(uint8_t v) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(v), __NV_E4M3);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+// Order-preserving map fp32 -> u32: a > b (as floats, -0 < +0) <=> key(a) > key(b).
+__device__ __forceinline__ uint32_t float_to_ordered(float f) {
+  uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+}  // namespace dsa

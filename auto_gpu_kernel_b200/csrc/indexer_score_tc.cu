@@ -1,0 +1,361 @@
+// FP8 indexer scorer on the 5th-generation tensor cores (tcgen05 kind::f8f6f4, TMEM accumulators).
+//
+//   score[b,t] = scale[t] * sum_h w[b,h] * relu( q[b,h,:] . k[t,:] )
+// (reference arithmetic: indexer_baseline.py:75-80; kernels this replaces: score_kernel of
+//  indexer_fused.py:80-158 and the Gluon _g_score_kernel of archive/fable/dsa_topk_indexer_*.py).
+//
+// Decode is bound by the HBM stream of the paged key cache (132 bytes per cached token), so the
+// kernel is a persistent, warp-specialised pipeline that keeps many pages in flight per SM:
+//
+//   warp 0  producer : walks its share of (request, 128-token tile) work items, looks the two pages
+//                      of a tile up in block_table (32 tiles per coalesced lookup) and issues, per
+//                      page, one 2-D TMA box (64 rows x 128 B, 128-byte swizzle) for the keys and one
+//                      256-byte bulk copy for the fp32 scales, into an 8-deep shared-memory ring;
+//   warp 1  MMA      : per tile 4 x tcgen05.mma M=128 (tokens) x N=64 (heads) x K=32, A = key tile,
+//                      B = the request's q (both K-major in shared memory), D in one of 4 TMEM
+//                      accumulator slots; tcgen05.commit releases the ring slot and publishes D;
+//   warps 2-5 epilogue: tcgen05.ld of the token's 64 head sums, relu, dot with w, times the token
+//                      scale, one coalesced fp32 store per token.
+//
+// Work is split evenly in tiles (not requests) across CTAs using an in-kernel prefix sum of the
+// device-resident seq_lens, so ragged batches balance without a host synchronisation.
+// Every mbarrier wait is time-bounded; on expiry the CTA records DSA_STATUS_WAIT_TIMEOUT, lets
+// copies in flight land, frees its TMEM and returns.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace dsa {
+
+constexpr int kTcStages = 8;
+constexpr int kTcAcc = 4;
+constexpr int kTcTile = 128;
+constexpr int kTcThreads = 192;
+constexpr int kTcMaxBatch = 4096;
+constexpr int kTcTmemCols = 256;            // 4 accumulators x 64 fp32 columns
+constexpr int kTileDataBytes = 2 * kPageDataBytes;  // 16384
+constexpr uint32_t kIdescF8 = ptx::idesc(ptx::kFmtE4M3, ptx::kFmtE4M3, false, false, 128, 64);
+
+struct TcShared {
+  // data[stage] and q[slot] sit in the 1024-byte aligned dynamic region before this struct
+  float scale[kTcStages][kTcTile];
+  int prefix[kTcMaxBatch + 1];
+  int partial[kTcThreads];
+  uint64_t full[kTcStages], empty[kTcStages];
+  uint64_t qfull[2], qempty[2];
+  uint64_t accfull[kTcAcc], accempty[kTcAcc];
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+constexpr size_t kTcDynBytes = 1024 + (size_t)kTcStages * kTileDataBytes + 2 * kPageDataBytes +
+                               sizeof(TcShared);
+
+__device__ __forceinline__ int tiles_of(int len, int max_pages, int skip_short) {
+  len = max(0, min(len, max_pages * kPage));
+  if (skip_short && len <= kTopK) return 0;
+  return (len + kTcTile - 1) / kTcTile;
+}
+
+// Largest b with prefix[b] <= w (prefix is non-decreasing, prefix[batch] > w).
+__device__ __forceinline__ int locate(const int* prefix, int batch, int w) {
+  int lo = 0, hi = batch;
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (prefix[mid] <= w) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
+                        const __grid_constant__ CUtensorMap tmap_q,
+                        const uint8_t* __restrict__ k_cache, const float* __restrict__ weights,
+                        const int32_t* __restrict__ seq_lens,
+                        const int32_t* __restrict__ block_table, int64_t bt_stride,
+                        float* __restrict__ scores, int64_t score_stride, int batch, int num_pages,
+                        int max_pages, int skip_short, int32_t* status) {
+  extern __shared__ unsigned char dyn_raw[];
+  const uint32_t raw_addr = smem_u32(dyn_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  unsigned char* base = dyn_raw + pad;
+  const uint32_t data_addr = raw_addr + pad;                          // kTcStages x 16 KB
+  const uint32_t q_addr = data_addr + kTcStages * kTileDataBytes;      // 2 x 8 KB
+  TcShared& sh = *reinterpret_cast<TcShared*>(base + kTcStages * kTileDataBytes + 2 * kPageDataBytes);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  // ---- tiles per request -> exclusive prefix (all threads) ------------------------------------
+  {
+    const int chunk = (batch + kTcThreads - 1) / kTcThreads;
+    const int lo = min(batch, tid * chunk), hi = min(batch, lo + chunk);
+    int sum = 0;
+    for (int b = lo; b < hi; ++b) sum += tiles_of(seq_lens[b], max_pages, skip_short);
+    sh.partial[tid] = sum;
+    __syncthreads();
+    if (tid == 0) {
+      int run = 0;
+      for (int i = 0; i < kTcThreads; ++i) { int v = sh.partial[i]; sh.partial[i] = run; run += v; }
+      sh.prefix[batch] = run;
+      sh.abort_flag = 0;
+    }
+    __syncthreads();
+    int run = sh.partial[tid];
+    for (int b = lo; b < hi; ++b) {
+      sh.prefix[b] = run;
+      run += tiles_of(seq_lens[b], max_pages, skip_short);
+    }
+  }
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < kTcStages; ++i) {
+        ptx::mbar_init(smem_u32(&sh.full[i]), 1);
+        ptx::mbar_init(smem_u32(&sh.empty[i]), 1 + 4);  // MMA commit + 4 epilogue warps
+      }
+      for (int i = 0; i < 2; ++i) {
+        ptx::mbar_init(smem_u32(&sh.qfull[i]), 1);
+        ptx::mbar_init(smem_u32(&sh.qempty[i]), 1);
+      }
+      for (int i = 0; i < kTcAcc; ++i) {
+        ptx::mbar_init(smem_u32(&sh.accfull[i]), 1);
+        ptx::mbar_init(smem_u32(&sh.accempty[i]), 4);
+      }
+      ptx::fence_barrier_init();
+      ptx::prefetch_tensormap(&tmap_k);
+      ptx::prefetch_tensormap(&tmap_q);
+    }
+    __syncwarp();
+    ptx::tmem_alloc(smem_u32(&sh.tmem_base), kTcTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+
+  const int total = sh.prefix[batch];
+  const int per = (total + gridDim.x - 1) / gridDim.x;
+  const int w0 = min(total, (int)blockIdx.x * per), w1 = min(total, w0 + per);
+  const uint32_t tmem_base = sh.tmem_base;
+
+#define DSA_WAIT(bar, parity)                                  \
+  if (!ptx::mbar_wait(smem_u32(&(bar)), (parity))) {           \
+    sh.abort_flag = 1;                                         \
+    raise_status(status, DSA_STATUS_WAIT_TIMEOUT);             \
+  }
+
+  if (w0 < w1) {
+    if (warp == 0) {
+      // ======================= producer =======================
+      int stage = 0, phase = 0, qslot = 0, qphase = 0, cur_b = -1;
+      for (int w = w0; w < w1 && !sh.abort_flag; w += 32) {
+        const int wi = min(w + lane, w1 - 1);
+        const int bi = locate(sh.prefix, batch, wi);
+        const int ji = wi - sh.prefix[bi];
+        const int len = max(0, min(seq_lens[bi], max_pages * kPage));
+        const int n_pages = (len + kPage - 1) / kPage;
+        const int32_t* row = block_table + (size_t)bi * bt_stride + 2 * ji;
+        int p0 = row[0];
+        int p1 = (2 * ji + 1 < n_pages) ? row[1] : -1;
+        if (p0 < 0 || p0 >= num_pages) { raise_status(status, DSA_STATUS_BAD_PAGE); p0 = 0; }
+        if (p1 >= num_pages) { raise_status(status, DSA_STATUS_BAD_PAGE); p1 = 0; }
+        const int n = min(32, w1 - w);
+        for (int i = 0; i < n; ++i) {
+          const int tb = __shfl_sync(0xffffffffu, bi, i);
+          const int a0 = __shfl_sync(0xffffffffu, p0, i);
+          const int a1 = __shfl_sync(0xffffffffu, p1, i);
+          if (lane == 0 && !sh.abort_flag) {
+            if (tb != cur_b) {
+              DSA_WAIT(sh.qempty[qslot], qphase ^ 1);
+              ptx::mbar_expect_tx(smem_u32(&sh.qfull[qslot]), kPageDataBytes);
+              ptx::tma_load_2d(q_addr + qslot * kPageDataBytes, &tmap_q, 0, tb * kIdxHeads,
+                               smem_u32(&sh.qfull[qslot]));
+              cur_b = tb;
+              qslot ^= 1;
+              if (qslot == 0) qphase ^= 1;
+            }
+            DSA_WAIT(sh.empty[stage], phase ^ 1);
+            const uint32_t bar = smem_u32(&sh.full[stage]);
+            const uint32_t dst = data_addr + stage * kTileDataBytes;
+            const uint32_t sdst = smem_u32(&sh.scale[stage][0]);
+            ptx::mbar_expect_tx(bar, (a1 >= 0 ? 2 : 1) * kPageBytes);
+            ptx::tma_load_2d(dst, &tmap_k, 0, a0 * 66, bar);
+            ptx::bulk_load_1d(sdst, k_cache + (size_t)a0 * kPageBytes + kPageDataBytes, 256, bar);
+            if (a1 >= 0) {
+              ptx::tma_load_2d(dst + kPageDataBytes, &tmap_k, 0, a1 * 66, bar);
+              ptx::bulk_load_1d(sdst + 256, k_cache + (size_t)a1 * kPageBytes + kPageDataBytes, 256,
+                                bar);
+            }
+            if (++stage == kTcStages) { stage = 0; phase ^= 1; }
+          }
+          __syncwarp();
+        }
+      }
+    } else if (warp == 1) {
+      // ======================= MMA issuer =======================
+      if (lane == 0) {
+        int stage = 0, phase = 0, qslot = 0, qphase = 0, acc = 0, aphase = 0;
+        int b = locate(sh.prefix, batch, w0), cur_b = -1;
+        for (int w = w0; w < w1 && !sh.abort_flag; ++w) {
+          while (sh.prefix[b + 1] <= w) ++b;
+          if (b != cur_b) {
+            if (cur_b >= 0) {  // all MMAs reading the previous q are issued: free it on completion
+              ptx::tc_commit(smem_u32(&sh.qempty[qslot ^ 1]));
+            }
+            DSA_WAIT(sh.qfull[qslot], qphase);
+            cur_b = b;
+            qslot ^= 1;
+            if (qslot == 0) qphase ^= 1;
+          }
+          const uint32_t qbase = q_addr + (qslot ^ 1) * kPageDataBytes;
+          DSA_WAIT(sh.accempty[acc], aphase ^ 1);
+          DSA_WAIT(sh.full[stage], phase);
+          if (sh.abort_flag) break;
+          ptx::tc_fence_after();
+          const uint64_t adesc = ptx::smem_desc_sw128(data_addr + stage * kTileDataBytes, 16, 1024);
+          const uint64_t bdesc = ptx::smem_desc_sw128(qbase, 16, 1024);
+          const uint32_t d = tmem_base + acc * kIdxHeads;
+#pragma unroll
+          for (int k = 0; k < 4; ++k)  // K = 32 fp8 = 32 bytes per instruction -> +2 in 16 B units
+            ptx::mma_f8(d, adesc + 2 * k, bdesc + 2 * k, kIdescF8, k > 0);
+          ptx::tc_commit(smem_u32(&sh.empty[stage]));
+          ptx::tc_commit(smem_u32(&sh.accfull[acc]));
+          if (++stage == kTcStages) { stage = 0; phase ^= 1; }
+          if (++acc == kTcAcc) { acc = 0; aphase ^= 1; }
+        }
+      }
+      __syncwarp();
+    } else {
+      // ======================= epilogue =======================
+      const int quarter = warp & 3;
+      const int rowi = quarter * 32 + lane;
+      int stage = 0, phase = 0, acc = 0, aphase = 0;
+      int b = locate(sh.prefix, batch, w0), cur_b = -1, len = 0;
+      float wreg[kIdxHeads];
+      for (int w = w0; w < w1 && !sh.abort_flag; ++w) {
+        while (sh.prefix[b + 1] <= w) ++b;
+        if (b != cur_b) {
+          const float4* wp = reinterpret_cast<const float4*>(weights + (size_t)b * kIdxHeads);
+#pragma unroll
+          for (int i = 0; i < kIdxHeads / 4; ++i) {
+            float4 v = __ldg(wp + i);
+            wreg[4 * i] = v.x; wreg[4 * i + 1] = v.y; wreg[4 * i + 2] = v.z; wreg[4 * i + 3] = v.w;
+          }
+          len = max(0, min(seq_lens[b], max_pages * kPage));
+          cur_b = b;
+        }
+        const int j = w - sh.prefix[b];
+        DSA_WAIT(sh.full[stage], phase);
+        const float sc = sh.scale[stage][rowi];
+        DSA_WAIT(sh.accfull[acc], aphase);
+        if (sh.abort_flag) break;
+        ptx::tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kIdxHeads;
+        uint32_t r0[32], r1[32];
+        ptx::tmem_ld32(taddr, r0);
+        ptx::tmem_ld32(taddr + 32, r1);
+        ptx::tmem_wait_ld();
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::mbar_arrive(smem_u32(&sh.accempty[acc]));
+          ptx::mbar_arrive(smem_u32(&sh.empty[stage]));
+        }
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int h = 0; h < 32; ++h) {
+          s0 = fmaf(wreg[h], fmaxf(__uint_as_float(r0[h]), 0.f), s0);
+          s1 = fmaf(wreg[32 + h], fmaxf(__uint_as_float(r1[h]), 0.f), s1);
+        }
+        const int t = j * kTcTile + rowi;
+        if (t < len) scores[(size_t)b * score_stride + t] = (s0 + s1) * sc;
+        if (++stage == kTcStages) { stage = 0; phase ^= 1; }
+        if (++acc == kTcAcc) { acc = 0; aphase ^= 1; }
+      }
+    }
+  }
+#undef DSA_WAIT
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    if (sh.abort_flag) {
+      // let bulk copies that were already issued land before the CTA's shared memory is released
+      for (int i = 0; i < 64; ++i) __nanosleep(20000);
+    }
+    ptx::tmem_dealloc(tmem_base, kTcTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// rows x 128 bytes, box = 64 rows x 128 bytes, 128-byte swizzle
+static bool make_rows128_map(CUtensorMap* map, const void* base, uint64_t rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (enc == nullptr) return false;
+  cuuint64_t dims[2] = {128, rows};
+  cuuint64_t strides[1] = {128};
+  cuuint32_t box[2] = {128, 64};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+cudaError_t launch_indexer_score_tc(const void* q_fp8, const void* k_cache, const float* weights,
+                                    const int32_t* seq_lens, const int32_t* block_table,
+                                    int64_t bt_stride, float* scores, int64_t score_stride,
+                                    int batch, int num_pages, int max_pages, int skip_short,
+                                    int32_t* status, cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(indexer_score_tc_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kTcDynBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  CUtensorMap tmap_k;
+  if (!make_rows128_map(&tmap_k, k_cache, (uint64_t)num_pages * 66)) return cudaErrorInvalidValue;
+  for (int b0 = 0; b0 < batch; b0 += kTcMaxBatch) {
+    const int nb = min(kTcMaxBatch, batch - b0);
+    CUtensorMap tmap_q;
+    const uint8_t* qp = static_cast<const uint8_t*>(q_fp8) + (size_t)b0 * kIdxHeads * kIdxDim;
+    if (!make_rows128_map(&tmap_q, qp, (uint64_t)nb * kIdxHeads)) return cudaErrorInvalidValue;
+    indexer_score_tc_kernel<<<sm_count(), kTcThreads, kTcDynBytes, stream>>>(
+        tmap_k, tmap_q, static_cast<const uint8_t*>(k_cache), weights + (size_t)b0 * kIdxHeads,
+        seq_lens + b0, block_table + (size_t)b0 * bt_stride, bt_stride,
+        scores + (size_t)b0 * score_stride, score_stride, nb, num_pages, max_pages, skip_short,
+        status);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
+
+}  // namespace dsa

@@ -1,0 +1,121 @@
+/*
+ * dsa_b200 -- C ABI of the B200 (sm_100a) DeepSeek Sparse Attention hot path.
+ *
+ * The reference repository (Dogacel/auto-gpu-kernel) has no native code: its hot path is the pair
+ * of Python entry points `kernel(...)` that flashinfer-bench calls with CUDA tensors.  Each entry
+ * point below states which Python interface of the reference it stands behind.  All pointers are
+ * DEVICE pointers unless a name ends in `_host`; the caller owns every buffer; nothing is allocated
+ * per call; work is enqueued on `stream` (a cudaStream_t passed as void*) and the call returns
+ * without synchronising.
+ *
+ * Return value: 0 = enqueued; negative = argument error found on the host (DSA_ERR_*); positive =
+ * a cudaError_t raised by a launch.  Faults found on the device (a bounded wait that ran out, an
+ * out-of-range page id in a checked build) are OR-ed into the int32 word `status_dev` points to
+ * (may be NULL); the caller reads it when it chooses to synchronise.
+ */
+#ifndef DSA_B200_H_
+#define DSA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DSA_B200_ABI_VERSION 1
+
+#define DSA_PAGE_SIZE 64
+#define DSA_INDEX_HEADS 64
+#define DSA_INDEX_DIM 128
+#define DSA_INDEX_PAGE_BYTES 8448 /* 64*128 e4m3 bytes, then 64 fp32 scales */
+#define DSA_TOPK 2048
+#define DSA_ATTN_HEADS 16
+#define DSA_CKV_DIM 512
+#define DSA_KPE_DIM 64
+
+enum {
+  DSA_OK = 0,
+  DSA_ERR_NULL_POINTER = -1,
+  DSA_ERR_BAD_SHAPE = -2,
+  DSA_ERR_WORKSPACE_TOO_SMALL = -3,
+  DSA_ERR_MISALIGNED = -4,
+  DSA_ERR_UNSUPPORTED = -5
+};
+
+/* bits OR-ed into *status_dev by kernels */
+#define DSA_STATUS_WAIT_TIMEOUT 0x1u   /* a bounded mbarrier / flag wait gave up */
+#define DSA_STATUS_BAD_PAGE     0x2u   /* block_table entry outside [0, num_pages) (skipped) */
+#define DSA_STATUS_BAD_SLOT     0x4u   /* sparse index outside [0, num_slots) (treated as -1) */
+#define DSA_STATUS_TOPK_COUNT   0x8u   /* selection wrote a number of ids != min(2048, len) */
+
+/* ABI version of the loaded library (DSA_B200_ABI_VERSION at build time). */
+int dsa_b200_version(void);
+
+/* Static text for a DSA_ERR_* code or a cudaError_t value returned by the calls below. */
+const char* dsa_b200_error_string(int code);
+
+/* ---------------------------------------------------------------------------------------------
+ * FP8 top-k indexer.  Stands behind the reference's
+ *   kernel(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table, topk_indices)
+ * (archive/dsa_topk_indexer_fp8_h64_d128_topk2048_ps64/solution/triton/indexer_baseline.py:39-90;
+ *  GPU dispatch it replaces: .../indexer_fused.py:331-412).
+ *
+ *   q_fp8        [batch,64,128] e4m3, contiguous
+ *   k_cache      [num_pages] pages of DSA_INDEX_PAGE_BYTES bytes (the [P,64,1,132] int8 tensor)
+ *   weights      [batch,64] fp32, contiguous
+ *   seq_lens     [batch] int32
+ *   block_table  [batch,max_pages] int32, row stride `block_table_stride` elements (0 = every
+ *                request shares one row: chunked prefill)
+ *   topk_out     [batch,2048] int32, row stride `topk_stride` elements; receives
+ *                min(2048,seq_len) global slot ids (page*64+offset) then -1
+ *   workspace    >= dsa_indexer_workspace_bytes(batch,max_pages) bytes, 256-byte aligned
+ * ------------------------------------------------------------------------------------------- */
+size_t dsa_indexer_workspace_bytes(int batch, int max_pages);
+
+int dsa_indexer_topk(const void* q_fp8, const void* k_cache, const float* weights,
+                     const int32_t* seq_lens, const int32_t* block_table,
+                     int64_t block_table_stride, int32_t* topk_out, int64_t topk_stride,
+                     int batch, int num_pages, int max_pages, void* workspace,
+                     size_t workspace_bytes, int32_t* status_dev, void* stream);
+
+/* Stage 1 alone: fp32 score rows, scores[b*score_stride + t] for t < seq_len[b] (the quantity
+ * `final_scores` of indexer_baseline.py:80).  Entries t >= seq_len[b] are left untouched.
+ * `variant`: 0 = tensor-core (tcgen05) scorer, 1 = plain CUDA-core scorer kept as an on-device
+ * cross-check. */
+int dsa_indexer_scores(const void* q_fp8, const void* k_cache, const float* weights,
+                       const int32_t* seq_lens, const int32_t* block_table,
+                       int64_t block_table_stride, float* scores, int64_t score_stride,
+                       int batch, int num_pages, int max_pages, int variant,
+                       int32_t* status_dev, void* stream);
+
+/* Stage 2 alone: top-2048 selection + page remap over given fp32 score rows
+ * (torch.topk + remap of indexer_baseline.py:82-90). */
+int dsa_topk_select(const float* scores, int64_t score_stride, const int32_t* seq_lens,
+                    const int32_t* block_table, int64_t block_table_stride, int32_t* topk_out,
+                    int64_t topk_stride, int batch, int max_pages, int32_t* status_dev,
+                    void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Sparse MLA attention.  Stands behind the reference's
+ *   kernel(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale, output, lse)
+ * (archive/dsa_sparse_attention_h16_ckv512_kpe64_topk2048_ps64/solution/triton/
+ *  sparse_baseline.py:12-45; GPU dispatch it replaces: .../sparse_fused.py:305-375).
+ *
+ *   q_nope  [tokens,heads,512] bf16   q_pe [tokens,heads,64] bf16      (contiguous)
+ *   ckv     [num_slots,512] bf16      kpe  [num_slots,64] bf16         (flat paged caches)
+ *   sparse_indices [tokens,topk] int32, row stride `index_stride`; -1 = masked
+ *   out     [tokens,heads,512] bf16   lse [tokens,heads] fp32 (base-2 log-sum-exp)
+ * A row with no valid index gets out = 0 and lse = -inf.  `heads` must be 16.
+ * ------------------------------------------------------------------------------------------- */
+size_t dsa_sparse_attn_workspace_bytes(int tokens, int heads, int topk);
+
+int dsa_sparse_attn(const void* q_nope, const void* q_pe, const void* ckv, const void* kpe,
+                    const int32_t* sparse_indices, int64_t index_stride, float sm_scale,
+                    void* out, float* lse, int tokens, int heads, int topk, int64_t num_slots,
+                    void* workspace, size_t workspace_bytes, int32_t* status_dev, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSA_B200_H_ */
