@@ -16,6 +16,10 @@ cudaError_t launch_topk_select(const float*, int64_t, const int32_t*, const int3
 cudaError_t launch_sparse_attn_simt(const void*, const void*, const void*, const void*,
                                     const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
                                     int, void*, int32_t*, cudaStream_t);
+cudaError_t launch_sparse_attn_tc(const void*, const void*, const void*, const void*,
+                                  const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
+                                  void*, int32_t*, cudaStream_t);
+size_t at_tc_workspace_bytes_auto(int tokens, int topk);
 int att_pick_splits(int tokens, int topk);
 size_t att_workspace_bytes(int tokens, int splits);
 }  // namespace dsa
@@ -123,14 +127,16 @@ int dsa_indexer_topk(const void* q_fp8, const void* k_cache, const float* weight
 }
 
 size_t dsa_sparse_attn_workspace_bytes(int tokens, int heads, int topk) {
-  if (tokens <= 0 || heads != dsa::kHeads) return 256;
-  return round256(dsa::att_workspace_bytes(tokens, dsa::att_pick_splits(tokens, topk)));
+  if (tokens <= 0 || heads != dsa::kHeads || topk <= 0) return 256;
+  size_t a = dsa::att_workspace_bytes(tokens, dsa::att_pick_splits(tokens, topk));
+  size_t b = dsa::at_tc_workspace_bytes_auto(tokens, topk);
+  return round256(a > b ? a : b);
 }
 
-int dsa_sparse_attn(const void* q_nope, const void* q_pe, const void* ckv, const void* kpe,
-                    const int32_t* sparse_indices, int64_t index_stride, float sm_scale, void* out,
-                    float* lse, int tokens, int heads, int topk, int64_t num_slots, void* workspace,
-                    size_t workspace_bytes, int32_t* status_dev, void* stream) {
+static int attn_impl(const void* q_nope, const void* q_pe, const void* ckv, const void* kpe,
+                     const int32_t* sparse_indices, int64_t index_stride, float sm_scale, void* out,
+                     float* lse, int tokens, int heads, int topk, int64_t num_slots, void* workspace,
+                     size_t workspace_bytes, int32_t* status_dev, void* stream, int variant) {
   if (tokens == 0) return DSA_OK;
   if (!q_nope || !q_pe || !ckv || !kpe || !sparse_indices || !out || !lse || !workspace)
     return DSA_ERR_NULL_POINTER;
@@ -141,10 +147,34 @@ int dsa_sparse_attn(const void* q_nope, const void* q_pe, const void* ckv, const
     return DSA_ERR_MISALIGNED;
   if (workspace_bytes < dsa_sparse_attn_workspace_bytes(tokens, heads, topk))
     return DSA_ERR_WORKSPACE_TOO_SMALL;
-  const int splits = dsa::att_pick_splits(tokens, topk);
-  return static_cast<int>(dsa::launch_sparse_attn_simt(
-      q_nope, q_pe, ckv, kpe, sparse_indices, index_stride, sm_scale, out, lse, tokens, topk,
-      num_slots, splits, workspace, status_dev, static_cast<cudaStream_t>(stream)));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (variant == 1) {
+    const int splits = dsa::att_pick_splits(tokens, topk);
+    return static_cast<int>(dsa::launch_sparse_attn_simt(q_nope, q_pe, ckv, kpe, sparse_indices,
+                                                         index_stride, sm_scale, out, lse, tokens,
+                                                         topk, num_slots, splits, workspace,
+                                                         status_dev, s));
+  }
+  return static_cast<int>(dsa::launch_sparse_attn_tc(q_nope, q_pe, ckv, kpe, sparse_indices,
+                                                     index_stride, sm_scale, out, lse, tokens, topk,
+                                                     num_slots, workspace, status_dev, s));
+}
+
+int dsa_sparse_attn(const void* q_nope, const void* q_pe, const void* ckv, const void* kpe,
+                    const int32_t* sparse_indices, int64_t index_stride, float sm_scale, void* out,
+                    float* lse, int tokens, int heads, int topk, int64_t num_slots, void* workspace,
+                    size_t workspace_bytes, int32_t* status_dev, void* stream) {
+  return attn_impl(q_nope, q_pe, ckv, kpe, sparse_indices, index_stride, sm_scale, out, lse, tokens,
+                   heads, topk, num_slots, workspace, workspace_bytes, status_dev, stream, 0);
+}
+
+int dsa_sparse_attn_cuda_core(const void* q_nope, const void* q_pe, const void* ckv,
+                              const void* kpe, const int32_t* sparse_indices, int64_t index_stride,
+                              float sm_scale, void* out, float* lse, int tokens, int heads, int topk,
+                              int64_t num_slots, void* workspace, size_t workspace_bytes,
+                              int32_t* status_dev, void* stream) {
+  return attn_impl(q_nope, q_pe, ckv, kpe, sparse_indices, index_stride, sm_scale, out, lse, tokens,
+                   heads, topk, num_slots, workspace, workspace_bytes, status_dev, stream, 1);
 }
 
 }  // extern "C"

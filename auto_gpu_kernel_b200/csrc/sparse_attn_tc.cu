@@ -1,0 +1,596 @@
+// Sparse MLA attention over the selected rows on the 5th-generation tensor cores.
+//
+//   logit[h,k] = (q_nope[h].ckv[idx[k]] + q_pe[h].kpe[idx[k]]) * sm_scale      idx == -1 -> masked
+//   lse[h]     = log2( sum_k e^{logit[h,k]} )          out[h] = softmax_k(logit[h,:]) @ ckv[idx[:]]
+// (reference arithmetic: sparse_baseline.py:18-45; kernels this replaces: sparse_fused.py:23-285 and
+//  the Gluon _dsa_decode_gluon of archive/fable/dsa_sparse_attention_*.py:77-433).
+//
+// Decode is bound by the HBM gather of 2048 random rows (1024 B ckv + 128 B kpe) per token, so the
+// design goal is bytes in flight; the 16 heads share every gathered row.
+//
+// Heads (16) are far below the tcgen05 M minimum, so the products are issued transposed: the
+// gathered rows are the M dimension and the heads are N = 16.
+//   S^T[64 rows,16]   = K[64,576] . Q^T            A = gathered tile, K-major; B = q, K-major
+//   O^T[512,16]      += V^T[512,64] . P^T          A = the SAME shared-memory tile read MN-major
+//                                                  (V is the 512-wide ckv part of the row);
+//                                                  B = P^T[16,64] bf16 written by the softmax warps
+// Shared-memory tile layout (one stage = 64 rows): nine [64 rows x 128 B] blocks (eight ckv column
+// blocks, one kpe block), each in the canonical 128-byte-swizzle layout, so one gather feeds both
+// products.
+//
+// Work split: the (token, 64-row tile) sequence is cut into equal contiguous ranges, one per CTA
+// (one CTA per SM), so SMs are balanced even when tokens x splits does not divide the SM count.  A
+// CTA's range covers parts ("segments") of at most a few tokens; a token covered by several CTAs is
+// merged by whichever of them finishes last (atomic arrival counter, nobody waits).
+//
+// Warp roles (288 threads): warps 0-3 softmax + epilogue (TMEM lane quarter = warp), warp 4 MMA
+// issuer, warps 5-8 gather producers (cp.async 16 B with zero-fill for masked rows, two stages).
+// The running max is only refreshed (and O rescaled in TMEM) when a logit exceeds it by more than
+// 2^8, so the common tile costs one exp2 per logit and no cross-thread reduction; row sums stay
+// per-thread until the end of the segment.  All waits are time-bounded; group decisions are taken
+// by one thread and broadcast, so a timeout makes every role leave together.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace dsa {
+
+constexpr int kAtTile = 64;
+constexpr int kAtBlockBytes = kAtTile * 128;       // 8192
+constexpr int kAtStageBytes = 9 * kAtBlockBytes;   // 73728
+constexpr int kAtQBlockBytes = kHeads * 128;       // 2048
+constexpr int kAtQBytes = 9 * kAtQBlockBytes;      // 18432
+constexpr int kAtPBytes = kHeads * 128;            // 2048
+constexpr int kAtThreads = 288;
+constexpr int kAtTmemCols = 128;
+constexpr int kAtSCol = 64;                        // S^T buffers at columns 64 and 96; O^T at 0..63
+constexpr float kAtLog2e = 1.4426950408889634f;
+constexpr float kAtRescaleGap = 8.f;
+constexpr uint32_t kIdescQK = ptx::idesc(ptx::kFmtBF16, ptx::kFmtBF16, false, false, 64, 16);
+constexpr uint32_t kIdescPV = ptx::idesc(ptx::kFmtBF16, ptx::kFmtBF16, true, false, 128, 16);
+
+struct AtShared {
+  int idx[2][kAtTile];
+  int any_live[2][4];
+  int live[2];
+  int need[4];
+  float red[4][kHeads];
+  int go[2][2];
+  uint64_t kv_full[2], kv_empty[2], q_full[2], q_empty[2];
+  uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_ready, o_free;
+  uint32_t tmem_base;
+  volatile int abort_flag;
+  int is_last;
+};
+
+constexpr size_t kAtDynBytes = 1024 + 2 * kAtStageBytes + 2 * kAtQBytes + 2 * kAtPBytes + sizeof(AtShared);
+
+struct AtPlan {
+  int tiles_per_token;  // ceil(topk / 64)
+  int per_cta;          // tiles per CTA range
+  int grid;
+  int segs_max;         // partial slots per token in the workspace
+};
+
+struct AtPartials {
+  int32_t* counters;  // [tokens], zero between calls
+  float* m;           // [tokens][segs_max][16]
+  float* l;           // [tokens][segs_max][16]
+  float* acc;         // [tokens][segs_max][16][512]
+};
+
+__host__ __device__ inline size_t at_counter_bytes(int tokens) {
+  return (((size_t)tokens * 4 + 255) / 256) * 256;
+}
+__host__ __device__ inline AtPartials at_carve(void* ws, int tokens, int segs_max) {
+  AtPartials w;
+  char* p = static_cast<char*>(ws);
+  w.counters = reinterpret_cast<int32_t*>(p);
+  p += at_counter_bytes(tokens);
+  w.m = reinterpret_cast<float*>(p);
+  p += (size_t)tokens * segs_max * kHeads * 4;
+  w.l = reinterpret_cast<float*>(p);
+  p += (size_t)tokens * segs_max * kHeads * 4;
+  w.acc = reinterpret_cast<float*>(p);
+  return w;
+}
+
+AtPlan at_make_plan(int tokens, int topk, int sms) {
+  AtPlan p;
+  p.tiles_per_token = (topk + kAtTile - 1) / kAtTile;
+  const long total = (long)tokens * p.tiles_per_token;
+  p.grid = (int)(total < sms ? total : sms);
+  if (p.grid < 1) p.grid = 1;
+  if (tokens >= 4 * p.grid) {  // whole tokens per CTA: no partial results at all
+    p.per_cta = p.tiles_per_token * ((tokens + p.grid - 1) / p.grid);
+    p.segs_max = 1;
+  } else {
+    p.per_cta = (int)((total + p.grid - 1) / p.grid);
+    int s = (p.tiles_per_token + p.per_cta - 1) / p.per_cta + 1;
+    p.segs_max = s < p.tiles_per_token ? s : p.tiles_per_token;
+  }
+  p.grid = (int)((total + p.per_cta - 1) / p.per_cta);
+  return p;
+}
+
+size_t at_tc_workspace_bytes(int tokens, int topk, int sms) {
+  AtPlan p = at_make_plan(tokens, topk, sms);
+  return at_counter_bytes(tokens) + (size_t)tokens * p.segs_max * kHeads * (2 + kCkv) * 4;
+}
+
+// One thread of a 128-thread group waits on an mbarrier (bounded) and the whole group learns the
+// outcome through shared memory, so that a timeout makes all of them leave the loop together.
+__device__ __forceinline__ bool group_wait(AtShared& sh, int group, int& toggle, bool leader,
+                                           uint32_t bar, uint32_t parity, int bar_id,
+                                           int32_t* status) {
+  if (leader) {
+    bool ok = !sh.abort_flag && ptx::mbar_wait(bar, parity);
+    if (!ok && !sh.abort_flag) {
+      sh.abort_flag = 1;
+      raise_status(status, DSA_STATUS_WAIT_TIMEOUT);
+    }
+    sh.go[group][toggle] = ok ? 1 : 0;
+  }
+  ptx::named_bar_sync(bar_id, 128);
+  const bool go = sh.go[group][toggle] != 0;
+  toggle ^= 1;
+  return go;
+}
+
+__device__ void at_merge_segments(const AtPartials& w, int t, int n_seg, int segs_max,
+                                  __nv_bfloat16* out, float* lse, int tid) {
+  // 128 threads: head = tid / 8, 64 output columns each
+  const int h = tid >> 3, c0 = (tid & 7) * 64;
+  float mx = -INFINITY;
+  for (int s = 0; s < n_seg; ++s) mx = fmaxf(mx, w.m[((size_t)t * segs_max + s) * kHeads + h]);
+  float lsum = 0.f;
+  float f[8];
+  for (int s = 0; s < n_seg; ++s) {
+    size_t o = ((size_t)t * segs_max + s) * kHeads + h;
+    float ms = w.m[o];
+    float fs = (ms == -INFINITY) ? 0.f : exp2f(ms - mx);
+    if (s < 8) f[s] = fs;
+    lsum += w.l[o] * fs;
+  }
+  const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+  __nv_bfloat16* dst = out + ((size_t)t * kHeads + h) * kCkv + c0;
+  for (int j = 0; j < 64; j += 4) {
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < n_seg; ++s) {
+      size_t o = ((size_t)t * segs_max + s) * kHeads + h;
+      float fs;
+      if (s < 8) fs = f[s];
+      else { float ms = w.m[o]; fs = (ms == -INFINITY) ? 0.f : exp2f(ms - mx); }
+      if (fs == 0.f) continue;
+      float4 v = *reinterpret_cast<const float4*>(w.acc + o * kCkv + c0 + j);
+      a.x += v.x * fs; a.y += v.y * fs; a.z += v.z * fs; a.w += v.w * fs;
+    }
+    *reinterpret_cast<__nv_bfloat162*>(dst + j) = __floats2bfloat162_rn(a.x * inv, a.y * inv);
+    *reinterpret_cast<__nv_bfloat162*>(dst + j + 2) = __floats2bfloat162_rn(a.z * inv, a.w * inv);
+  }
+  if ((tid & 7) == 0) {
+    lse[(size_t)t * kHeads + h] = lsum > 0.f ? mx + log2f(lsum) : -INFINITY;
+  }
+}
+
+__global__ void __launch_bounds__(kAtThreads, 1)
+sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloat16* __restrict__ q_pe,
+                      const __nv_bfloat16* __restrict__ ckv, const __nv_bfloat16* __restrict__ kpe,
+                      const int32_t* __restrict__ indices, int64_t index_stride, float scale_log2,
+                      __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int tokens, int topk,
+                      int64_t num_slots, AtPlan plan, void* ws_raw, int32_t* status) {
+  extern __shared__ unsigned char dyn_raw[];
+  const uint32_t raw_addr = smem_u32(dyn_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  const uint32_t kv_addr = raw_addr + pad;                 // 2 stages
+  const uint32_t q_addr = kv_addr + 2 * kAtStageBytes;     // 2 q buffers
+  const uint32_t p_addr = q_addr + 2 * kAtQBytes;          // 2 P^T buffers
+  unsigned char* p_ptr = dyn_raw + pad + 2 * kAtStageBytes + 2 * kAtQBytes;
+  AtShared& sh = *reinterpret_cast<AtShared*>(p_ptr + 2 * kAtPBytes);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tpt = plan.tiles_per_token;
+  const long total = (long)tokens * tpt;
+  const long w0 = (long)blockIdx.x * plan.per_cta;
+  const long w1 = w0 + plan.per_cta < total ? w0 + plan.per_cta : total;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      for (int i = 0; i < 2; ++i) {
+        ptx::mbar_init(smem_u32(&sh.kv_full[i]), 128 + 1);
+        ptx::mbar_init(smem_u32(&sh.kv_empty[i]), 2);
+        ptx::mbar_init(smem_u32(&sh.q_full[i]), 128);
+        ptx::mbar_init(smem_u32(&sh.q_empty[i]), 1);
+        ptx::mbar_init(smem_u32(&sh.s_full[i]), 1);
+        ptx::mbar_init(smem_u32(&sh.s_empty[i]), 4);
+        ptx::mbar_init(smem_u32(&sh.p_full[i]), 4);
+        ptx::mbar_init(smem_u32(&sh.p_empty[i]), 1);
+      }
+      ptx::mbar_init(smem_u32(&sh.o_ready), 1);
+      ptx::mbar_init(smem_u32(&sh.o_free), 4);
+      sh.abort_flag = 0;
+      ptx::fence_barrier_init();
+    }
+    __syncwarp();
+    ptx::tmem_alloc(smem_u32(&sh.tmem_base), kAtTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = sh.tmem_base;
+
+  if (w0 < w1) {
+    if (warp < 4) {
+      // =========================== softmax + epilogue ===========================
+      const bool leader = tid == 0;
+      const bool has_row = lane < 16;
+      const int row = warp * 16 + (lane & 15);
+      const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+      int toggle = 0, stage = 0, phase = 0, n = 0, seg_live = 0;
+      long cur_t = -1;
+      float m_run[kHeads], l_part[kHeads];
+      AtPartials part = at_carve(ws_raw, tokens, plan.segs_max);
+      for (long w = w0; w < w1; ++w) {
+        const long t = w / tpt;
+        const int j = (int)(w - t * tpt);
+        if (t != cur_t) {
+#pragma unroll
+          for (int h = 0; h < kHeads; ++h) { m_run[h] = -INFINITY; l_part[h] = 0.f; }
+          seg_live = 0;
+          cur_t = t;
+        }
+        if (!group_wait(sh, 0, toggle, leader, smem_u32(&sh.kv_full[stage]), phase, 1, status)) break;
+        const bool live = sh.live[stage] != 0;
+        const bool valid = has_row && sh.idx[stage][row] >= 0;
+        ptx::named_bar_sync(1, 128);
+        if (leader) ptx::mbar_arrive(smem_u32(&sh.kv_empty[stage]));
+        stage ^= 1;
+        if (stage == 0) phase ^= 1;
+        if (live) {
+          const int sbuf = n & 1, sphase = (n >> 1) & 1;
+          if (!group_wait(sh, 0, toggle, leader, smem_u32(&sh.s_full[sbuf]), sphase, 1, status)) break;
+          ptx::tc_fence_after();
+          uint32_t sr[16];
+          ptx::tmem_ld16(tmem_base + lane_base + kAtSCol + sbuf * 32, sr);
+          ptx::tmem_wait_ld();
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(smem_u32(&sh.s_empty[sbuf]));
+          float x[kHeads];
+          bool need = false;
+#pragma unroll
+          for (int h = 0; h < kHeads; ++h) {
+            x[h] = valid ? __uint_as_float(sr[h]) * scale_log2 : -INFINITY;
+            need |= x[h] > m_run[h] + kAtRescaleGap;
+          }
+          const bool warp_need = __any_sync(0xffffffffu, need);
+          if (lane == 0) sh.need[warp] = warp_need;
+          ptx::named_bar_sync(1, 128);
+          if (sh.need[0] | sh.need[1] | sh.need[2] | sh.need[3]) {
+            // refresh the running max of every head, rescale what was accumulated so far
+#pragma unroll
+            for (int h = 0; h < kHeads; ++h) {
+              float v = x[h];
+#pragma unroll
+              for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+              if (lane == 0) sh.red[warp][h] = v;
+            }
+            ptx::named_bar_sync(1, 128);
+            float corr[kHeads];
+#pragma unroll
+            for (int h = 0; h < kHeads; ++h) {
+              float mx = fmaxf(fmaxf(sh.red[0][h], sh.red[1][h]), fmaxf(sh.red[2][h], sh.red[3][h]));
+              float m_new = fmaxf(m_run[h], mx);
+              corr[h] = m_new == -INFINITY ? 1.f : exp2f(m_run[h] - m_new);
+              m_run[h] = m_new;
+              l_part[h] *= corr[h];
+            }
+            if (seg_live > 0) {
+              if (!group_wait(sh, 0, toggle, leader, smem_u32(&sh.o_ready), (n - 1) & 1, 1, status)) break;
+              ptx::tc_fence_after();
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                uint32_t o[16];
+                ptx::tmem_ld16(tmem_base + lane_base + c * 16, o);
+                ptx::tmem_wait_ld();
+#pragma unroll
+                for (int h = 0; h < kHeads; ++h) o[h] = __float_as_uint(__uint_as_float(o[h]) * corr[h]);
+                ptx::tmem_st16(tmem_base + lane_base + c * 16, o);
+              }
+              ptx::tmem_wait_st();
+              ptx::tc_fence_before();
+            }
+          }
+          if (!group_wait(sh, 0, toggle, leader, smem_u32(&sh.p_empty[sbuf]), sphase ^ 1, 1, status)) break;
+          if (has_row) {
+            unsigned char* pb = p_ptr + sbuf * kAtPBytes;
+#pragma unroll
+            for (int h = 0; h < kHeads; ++h) {
+              const float m_use = m_run[h] == -INFINITY ? 0.f : m_run[h];
+              const float p = exp2f(x[h] - m_use);
+              l_part[h] += p;
+              *reinterpret_cast<__nv_bfloat16*>(pb + h * 128 + ((((row >> 3) ^ (h & 7)) & 7) << 4) +
+                                                (row & 7) * 2) = __float2bfloat16_rn(p);
+            }
+          }
+          ptx::fence_proxy_async_smem();
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(smem_u32(&sh.p_full[sbuf]));
+          ++n;
+          ++seg_live;
+        }
+        if (j == tpt - 1 || w == w1 - 1) {
+          // ------------------ end of this CTA's segment of token t ------------------
+          if (seg_live > 0) {
+            if (!group_wait(sh, 0, toggle, leader, smem_u32(&sh.o_ready), (n - 1) & 1, 1, status)) break;
+            ptx::tc_fence_after();
+          }
+#pragma unroll
+          for (int h = 0; h < kHeads; ++h) {
+            float v = has_row ? l_part[h] : 0.f;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) sh.red[warp][h] = v;
+          }
+          ptx::named_bar_sync(1, 128);
+          float l_tot[kHeads];
+#pragma unroll
+          for (int h = 0; h < kHeads; ++h)
+            l_tot[h] = (sh.red[0][h] + sh.red[1][h]) + (sh.red[2][h] + sh.red[3][h]);
+          const long first_tile = t * tpt, last_tile = first_tile + tpt - 1;
+          const int cta_first = (int)(first_tile / plan.per_cta), cta_last = (int)(last_tile / plan.per_cta);
+          const int n_seg = cta_last - cta_first + 1, seg = (int)blockIdx.x - cta_first;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[16];
+            if (seg_live > 0) {
+              ptx::tmem_ld16(tmem_base + lane_base + c * 16, o);
+              ptx::tmem_wait_ld();
+            } else {
+#pragma unroll
+              for (int h = 0; h < kHeads; ++h) o[h] = 0u;
+            }
+            const int dim = c * 128 + warp * 32 + lane;
+            if (n_seg == 1) {
+#pragma unroll
+              for (int h = 0; h < kHeads; ++h) {
+                const float inv = l_tot[h] > 0.f ? 1.f / l_tot[h] : 0.f;
+                out[((size_t)t * kHeads + h) * kCkv + dim] = __float2bfloat16_rn(__uint_as_float(o[h]) * inv);
+              }
+            } else {
+#pragma unroll
+              for (int h = 0; h < kHeads; ++h)
+                part.acc[(((size_t)t * plan.segs_max + seg) * kHeads + h) * kCkv + dim] = __uint_as_float(o[h]);
+            }
+          }
+          if (tid < kHeads) {
+            // m_run / l_tot are identical in every thread; pick head `tid` without dynamic indexing
+            float mh = 0.f, lh = 0.f;
+#pragma unroll
+            for (int h = 0; h < kHeads; ++h) if (h == tid) { mh = m_run[h]; lh = l_tot[h]; }
+            if (n_seg == 1) {
+              lse[(size_t)t * kHeads + tid] = lh > 0.f ? mh + log2f(lh) : -INFINITY;
+            } else {
+              part.m[((size_t)t * plan.segs_max + seg) * kHeads + tid] = lh > 0.f ? mh : -INFINITY;
+              part.l[((size_t)t * plan.segs_max + seg) * kHeads + tid] = lh;
+            }
+          }
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(smem_u32(&sh.o_free));
+          if (n_seg > 1) {
+            __threadfence();
+            ptx::named_bar_sync(1, 128);
+            if (leader) {
+              const int old = atomicAdd(&part.counters[t], 1);
+              sh.is_last = old == n_seg - 1;
+              if (sh.is_last) part.counters[t] = 0;
+            }
+            ptx::named_bar_sync(1, 128);
+            if (sh.is_last) {
+              __threadfence();
+              at_merge_segments(part, (int)t, n_seg, plan.segs_max, out, lse, tid);
+            }
+          }
+        }
+      }
+    } else if (warp == 4) {
+      // =========================== MMA issuer ===========================
+      if (lane == 0) {
+        int stage = 0, phase = 0, nq = 0, np = 0, seg_no = 0, qb = 0, qphase = 0, qcur = 0;
+        long cur_t = -1;
+        bool pend = false, pend_first = false, seg_first = true, ok = true;
+        int pend_stage = 0;
+#define AT_WAIT(bar, parity)                                          \
+  if (ok && !(!sh.abort_flag && ptx::mbar_wait(smem_u32(&(bar)), (parity)))) { \
+    if (!sh.abort_flag) { sh.abort_flag = 1; raise_status(status, DSA_STATUS_WAIT_TIMEOUT); } \
+    ok = false;                                                       \
+  }
+        auto issue_pv = [&]() {
+          const int pbuf = np & 1, pphase = (np >> 1) & 1;
+          AT_WAIT(sh.p_full[pbuf], pphase);
+          if (!ok) return;
+          ptx::tc_fence_after();
+          const uint32_t a0 = kv_addr + pend_stage * kAtStageBytes;
+          const uint32_t b0 = p_addr + pbuf * kAtPBytes;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              const uint64_t ad = ptx::smem_desc_sw128(a0 + 2 * c * kAtBlockBytes + ks * 2048, kAtBlockBytes, 1024);
+              const uint64_t bd = ptx::smem_desc_sw128(b0 + ks * 32, 16, 1024);
+              ptx::mma_bf16(tmem_base + c * 16, ad, bd, kIdescPV, !(pend_first && ks == 0));
+            }
+          }
+          ptx::tc_commit(smem_u32(&sh.kv_empty[pend_stage]));
+          ptx::tc_commit(smem_u32(&sh.p_empty[pbuf]));
+          ptx::tc_commit(smem_u32(&sh.o_ready));
+          ++np;
+          pend = false;
+        };
+        for (long w = w0; w < w1 && ok; ++w) {
+          const long t = w / tpt;
+          if (t != cur_t) {
+            if (cur_t >= 0) {
+              if (pend) issue_pv();
+              ptx::tc_commit(smem_u32(&sh.q_empty[qcur]));
+              AT_WAIT(sh.o_free, seg_no & 1);  // epilogue of the previous segment has read O^T
+              ++seg_no;
+            }
+            AT_WAIT(sh.q_full[qb], qphase);
+            qcur = qb;
+            qb ^= 1;
+            if (qb == 0) qphase ^= 1;
+            cur_t = t;
+            seg_first = true;
+          }
+          AT_WAIT(sh.kv_full[stage], phase);
+          if (!ok) break;
+          ptx::fence_proxy_async_smem();  // cp.async-written tile / q -> visible to the MMA's reads
+          if (sh.live[stage]) {
+            const int sbuf = nq & 1, sphase = (nq >> 1) & 1;
+            AT_WAIT(sh.s_empty[sbuf], sphase ^ 1);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const uint32_t a0 = kv_addr + stage * kAtStageBytes;
+            const uint32_t b0 = q_addr + qcur * kAtQBytes;
+#pragma unroll
+            for (int kb = 0; kb < 9; ++kb) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const uint64_t ad = ptx::smem_desc_sw128(a0 + kb * kAtBlockBytes + k * 32, 16, 1024);
+                const uint64_t bd = ptx::smem_desc_sw128(b0 + kb * kAtQBlockBytes + k * 32, 16, 1024);
+                ptx::mma_bf16(tmem_base + kAtSCol + sbuf * 32, ad, bd, kIdescQK, (kb | k) != 0);
+              }
+            }
+            ptx::tc_commit(smem_u32(&sh.s_full[sbuf]));
+            ++nq;
+            if (pend) issue_pv();
+            pend = true;
+            pend_stage = stage;
+            pend_first = seg_first;
+            seg_first = false;
+          } else {
+            ptx::mbar_arrive(smem_u32(&sh.kv_empty[stage]));
+          }
+          stage ^= 1;
+          if (stage == 0) phase ^= 1;
+        }
+        if (pend && ok) issue_pv();
+#undef AT_WAIT
+      }
+      __syncwarp();
+    } else {
+      // =========================== gather producers ===========================
+      const int ptid = tid - 160, pwarp = ptid >> 5;
+      const bool leader = ptid == 0;
+      int toggle = 0, stage = 0, phase = 0, qb = 0, qphase = 0;
+      long cur_t = -1;
+      for (long w = w0; w < w1; ++w) {
+        const long t = w / tpt;
+        const int j = (int)(w - t * tpt);
+        if (t != cur_t) {
+          if (!group_wait(sh, 1, toggle, leader, smem_u32(&sh.q_empty[qb]), qphase ^ 1, 2, status)) break;
+          const uint32_t qdst = q_addr + qb * kAtQBytes;
+#pragma unroll
+          for (int it = 0; it < 9; ++it) {
+            const int c = it * 128 + ptid, h = c / 72, jj = c - h * 72;
+            const __nv_bfloat16* src = jj < 64 ? q_nope + ((size_t)(t * kHeads + h) * kCkv + jj * 8)
+                                               : q_pe + ((size_t)(t * kHeads + h) * kKpe + (jj - 64) * 8);
+            ptx::cp_async16(qdst + (jj >> 3) * kAtQBlockBytes + h * 128 + (((jj & 7) ^ (h & 7)) << 4), src, 16);
+          }
+          ptx::cp_async_arrive_noinc(smem_u32(&sh.q_full[qb]));
+          cur_t = t;
+          qb ^= 1;
+          if (qb == 0) qphase ^= 1;
+        }
+        int my = -1;
+        if (ptid < kAtTile) {
+          const int k = j * kAtTile + ptid;
+          if (k < topk) my = indices[(size_t)t * index_stride + k];
+          if (my >= num_slots) { raise_status(status, DSA_STATUS_BAD_SLOT); my = -1; }
+          if (my < 0) my = -1;
+        }
+        if (!group_wait(sh, 1, toggle, leader, smem_u32(&sh.kv_empty[stage]), phase ^ 1, 2, status)) break;
+        if (ptid < kAtTile) sh.idx[stage][ptid] = my;
+        const bool any = __any_sync(0xffffffffu, my >= 0);
+        if (lane == 0) sh.any_live[stage][pwarp] = any;
+        ptx::named_bar_sync(2, 128);
+        const bool live = (sh.any_live[stage][0] | sh.any_live[stage][1]) != 0;
+        if (live) {
+          const uint32_t dst0 = kv_addr + stage * kAtStageBytes;
+          int r = ptid / 72, jj = ptid - r * 72;
+#pragma unroll 4
+          for (int it = 0; it < 36; ++it) {
+            const int slot = sh.idx[stage][r];
+            const __nv_bfloat16* src = ckv;
+            if (slot >= 0)
+              src = jj < 64 ? ckv + ((size_t)slot * kCkv + jj * 8) : kpe + ((size_t)slot * kKpe + (jj - 64) * 8);
+            ptx::cp_async16(dst0 + (jj >> 3) * kAtBlockBytes + r * 128 + (((jj & 7) ^ (r & 7)) << 4), src,
+                            slot >= 0 ? 16u : 0u);
+            jj += 56; r += 1;
+            if (jj >= 72) { jj -= 72; r += 1; }
+          }
+        }
+        ptx::cp_async_arrive_noinc(smem_u32(&sh.kv_full[stage]));
+        if (leader) {
+          sh.live[stage] = live ? 1 : 0;
+          ptx::mbar_arrive(smem_u32(&sh.kv_full[stage]));
+        }
+        stage ^= 1;
+        if (stage == 0) phase ^= 1;
+      }
+      ptx::cp_async_wait_all();
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    if (sh.abort_flag) {
+      for (int i = 0; i < 64; ++i) __nanosleep(20000);
+    }
+    ptx::tmem_dealloc(tmem_base, kAtTmemCols);
+  }
+}
+
+static int at_sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = 0;
+      return 148;
+    }
+  }
+  return n;
+}
+
+size_t at_tc_workspace_bytes_auto(int tokens, int topk) {
+  return at_tc_workspace_bytes(tokens, topk, at_sm_count());
+}
+
+cudaError_t launch_sparse_attn_tc(const void* q_nope, const void* q_pe, const void* ckv,
+                                  const void* kpe, const int32_t* indices, int64_t index_stride,
+                                  float sm_scale, void* out, float* lse, int tokens, int topk,
+                                  int64_t num_slots, void* ws, int32_t* status, cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(sparse_attn_tc_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAtDynBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  const AtPlan plan = at_make_plan(tokens, topk, at_sm_count());
+  sparse_attn_tc_kernel<<<plan.grid, kAtThreads, kAtDynBytes, stream>>>(
+      static_cast<const __nv_bfloat16*>(q_nope), static_cast<const __nv_bfloat16*>(q_pe),
+      static_cast<const __nv_bfloat16*>(ckv), static_cast<const __nv_bfloat16*>(kpe), indices,
+      index_stride, sm_scale * kAtLog2e, static_cast<__nv_bfloat16*>(out), lse, tokens, topk,
+      num_slots, plan, ws, status);
+  return cudaGetLastError();
+}
+
+}  // namespace dsa

@@ -153,3 +153,32 @@ def uniform_lengths(count, lo, hi, seed=0):
     """`count` sequence lengths uniform in [lo, hi], seeded."""
     gen = torch.Generator(device="cpu").manual_seed(seed)
     return torch.randint(lo, hi + 1, (count,), generator=gen).tolist()
+
+
+@dataclass
+class DecodeBlockInputs:
+    """One decode step of the DSA block: the indexer picks 2048 slots per request, attention reads
+    them from ckv/kpe caches that share the index-key cache's page numbering."""
+    indexer: IndexerInputs
+    q_nope: torch.Tensor
+    q_pe: torch.Tensor
+    ckv_cache: torch.Tensor
+    kpe_cache: torch.Tensor
+    sm_scale: float
+
+
+def make_decode_block_inputs(seq_lens, seed=0, device="cpu", heads=ATTN_HEADS, chunk_pages=2048):
+    idx = make_indexer_inputs(seq_lens, seed=seed, device=device)
+    pages = idx.k_index_cache_fp8.shape[0]
+    dev = torch.device(device)
+    dgen = torch.Generator(device=dev).manual_seed(seed + 3)
+    ckv = torch.empty(pages, PAGE_SIZE, CKV_DIM, dtype=torch.bfloat16, device=dev)
+    kpe = torch.empty(pages, PAGE_SIZE, KPE_DIM, dtype=torch.bfloat16, device=dev)
+    for lo in range(0, pages, chunk_pages):
+        hi = min(lo + chunk_pages, pages)
+        ckv[lo:hi] = torch.randn(hi - lo, PAGE_SIZE, CKV_DIM, generator=dgen, device=dev).to(torch.bfloat16)
+        kpe[lo:hi] = torch.randn(hi - lo, PAGE_SIZE, KPE_DIM, generator=dgen, device=dev).to(torch.bfloat16)
+    tokens = len(seq_lens)
+    qn = (torch.randn(tokens, heads, CKV_DIM, generator=dgen, device=dev) * 0.1).to(torch.bfloat16)
+    qp = (torch.randn(tokens, heads, KPE_DIM, generator=dgen, device=dev) * 0.1).to(torch.bfloat16)
+    return DecodeBlockInputs(idx, qn, qp, ckv, kpe, 1.0 / math.sqrt(192.0))

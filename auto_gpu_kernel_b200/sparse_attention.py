@@ -18,7 +18,10 @@ CKV = 512
 KPE = 64
 
 
-def kernel(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale, output, lse):
+def kernel(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale, output, lse, variant=0):
+    """Write attention output and base-2 LSE in place; enqueued on the current stream, returns None.
+    `variant` 0 = tcgen05 kernel, 1 = CUDA-core cross-check kernel (not part of the reference
+    signature; positional callers never pass it)."""
     if not q_nope.is_cuda:
         raise RuntimeError("dsa sparse attention: CUDA tensors required (this operator has no CPU path)")
     dev = q_nope.device
@@ -55,7 +58,8 @@ def kernel(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale, output,
     need = lib.dsa_sparse_attn_workspace_bytes(tokens, HEADS, topk)
     ws = workspace.get(dev, "attention", need)
     with torch.cuda.device(dev):
-        rc = lib.dsa_sparse_attn(
+        fn = lib.dsa_sparse_attn if variant == 0 else lib.dsa_sparse_attn_cuda_core
+        rc = fn(
             q_nope.data_ptr(), q_pe.data_ptr(), ckv_cache.data_ptr(), kpe_cache.data_ptr(),
             sparse_indices.data_ptr(), sparse_indices.stride(0), float(sm_scale),
             output.data_ptr(), lse.data_ptr(), tokens, HEADS, topk, slots, ws.data_ptr(),
@@ -65,12 +69,13 @@ def kernel(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale, output,
     return None
 
 
-def run(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale, output=None, lse=None):
+def run(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale, output=None, lse=None,
+        variant=0):
     """Value-returning form: allocates the outputs that are not passed; returns (output, lse)."""
     tokens = q_nope.shape[0]
     if output is None:
         output = torch.empty(tokens, HEADS, CKV, dtype=torch.bfloat16, device=q_nope.device)
     if lse is None:
         lse = torch.empty(tokens, HEADS, dtype=torch.float32, device=q_nope.device)
-    kernel(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale, output, lse)
+    kernel(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale, output, lse, variant)
     return output, lse

@@ -9,25 +9,31 @@ from helpers import assert_attention_close, load_attention_golden
 pytestmark = pytest.mark.gpu
 
 
+VARIANTS = pytest.mark.parametrize("variant", [1, 0], ids=["cuda_core", "tcgen05"])
+
+
+@VARIANTS
 @pytest.mark.parametrize("name", ["attention_small", "attention_padded"])
-def test_matches_golden(cuda, name):
+def test_matches_golden(cuda, name, variant):
     inp, ref_out, ref_lse = load_attention_golden(name)
     dev = inp.to(cuda)
     out = torch.full_like(ref_out, 7.0, device=cuda)
     lse = torch.full_like(ref_lse, 7.0, device=cuda)
-    assert sparse_attention.kernel(*dev.args(), out, lse) is None
+    assert sparse_attention.kernel(*dev.args(), out, lse, variant) is None
     workspace.check_status(cuda)
     assert_attention_close(out, lse, ref_out, ref_lse, label=name)
-    out2, lse2 = sparse_attention.run(*dev.args())     # second call reuses the workspace counters
+    out2, lse2 = sparse_attention.run(*dev.args(), variant=variant)  # workspace counters reused
     assert_attention_close(out2, lse2, ref_out, ref_lse, label=name + "/again")
 
 
-@pytest.mark.parametrize("tokens", [1, 2, 8, 64, 300])
-def test_token_counts_against_gpu_oracle(cuda, tokens):
-    """Different token counts exercise different split counts of the selected rows."""
+@VARIANTS
+@pytest.mark.parametrize("tokens", [1, 2, 8, 64, 300, 700])
+def test_token_counts_against_gpu_oracle(cuda, tokens, variant):
+    """Different token counts exercise different splits of the selected rows across CTAs: many
+    segments per token (1, 2, 8), a few (64, 300), whole tokens per CTA (700)."""
     lens = wl.uniform_lengths(tokens, 2100, 6000, seed=tokens)
     inp = wl.make_attention_inputs(lens, seed=tokens, device=cuda)
-    out, lse = sparse_attention.run(*inp.args())
+    out, lse = sparse_attention.run(*inp.args(), variant=variant)
     workspace.check_status(cuda)
     ref_out, ref_lse = oracle.sparse_attention(
         *[a if not torch.is_tensor(a) else a for a in inp.args()],
@@ -35,7 +41,8 @@ def test_token_counts_against_gpu_oracle(cuda, tokens):
     assert_attention_close(out, lse, ref_out.cpu(), ref_lse.cpu(), label=f"T={tokens}")
 
 
-def test_interior_and_leading_padding(cuda):
+@VARIANTS
+def test_interior_and_leading_padding(cuda, variant):
     """-1 entries anywhere in a row (not only the tail) are masked."""
     inp = wl.make_attention_inputs([4000, 4000, 4000], seed=9, device=cuda)
     idx = inp.sparse_indices.clone()
@@ -43,34 +50,51 @@ def test_interior_and_leading_padding(cuda):
     idx[1, :1000] = -1
     idx[2, 5:] = -1
     inp.sparse_indices = idx
-    out, lse = sparse_attention.run(*inp.args())
+    out, lse = sparse_attention.run(*inp.args(), variant=variant)
     workspace.check_status(cuda)
     ref_out, ref_lse = oracle.sparse_attention(*inp.to("cpu").args())
     assert_attention_close(out, lse, ref_out, ref_lse, label="interior padding")
 
 
-def test_large_logits_are_stable(cuda):
+@VARIANTS
+def test_large_logits_are_stable(cuda, variant):
     """Scaled-up queries give logits far outside exp range: the online softmax must not overflow."""
     inp = wl.make_attention_inputs([3000, 2500], seed=4, device=cuda)
     inp.q_nope = (inp.q_nope.float() * 40).to(torch.bfloat16)
-    out, lse = sparse_attention.run(*inp.args())
+    out, lse = sparse_attention.run(*inp.args(), variant=variant)
     workspace.check_status(cuda)
     ref_out, ref_lse = oracle.sparse_attention(*inp.to("cpu").args())
     assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
     assert_attention_close(out, lse, ref_out, ref_lse, label="large logits")
 
 
-def test_out_of_range_slot_is_masked_and_reported(cuda):
+@VARIANTS
+def test_out_of_range_slot_is_masked_and_reported(cuda, variant):
     inp = wl.make_attention_inputs([2500], seed=6, device=cuda)
     slots = inp.ckv_cache.shape[0] * 64
     inp.sparse_indices[0, 7] = slots + 5
-    out, lse = sparse_attention.run(*inp.args())
+    out, lse = sparse_attention.run(*inp.args(), variant=variant)
     with pytest.raises(RuntimeError, match="sparse index outside"):
         workspace.check_status(cuda)
     cpu = inp.to("cpu")
     cpu.sparse_indices[0, 7] = -1
     ref_out, ref_lse = oracle.sparse_attention(*cpu.args())
     assert_attention_close(out, lse, ref_out, ref_lse, label="bad slot")
+
+
+def test_ascending_logits_force_rescales(cuda):
+    """Rows ordered so that logits grow tile after tile: the running max is refreshed repeatedly
+    and the accumulated output is rescaled in place many times."""
+    inp = wl.make_attention_inputs([4096], seed=12, device=cuda)
+    cpu = inp.to("cpu")
+    logits = (cpu.q_nope[0, 0].float() @ cpu.ckv_cache.reshape(-1, 512)[cpu.sparse_indices[0].long()].float().T)
+    order = torch.argsort(logits)                       # ascending for head 0
+    inp.sparse_indices[0] = inp.sparse_indices[0][order.to(cuda)]
+    inp.q_nope = (inp.q_nope.float() * 30).to(torch.bfloat16)
+    out, lse = sparse_attention.run(*inp.args())
+    workspace.check_status(cuda)
+    ref_out, ref_lse = oracle.sparse_attention(*inp.to("cpu").args())
+    assert_attention_close(out, lse, ref_out, ref_lse, label="ascending")
 
 
 def test_cpu_tensors_are_rejected():
