@@ -259,14 +259,19 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
           ptx::mbar_arrive(smem_u32(&sh.accempty[acc]));
           ptx::mbar_arrive(smem_u32(&sh.empty[stage]));
         }
-        float s0 = 0.f, s1 = 0.f;
+        // eight independent partial sums: the FMA chain per sum is 8 long instead of 64
+        float part[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) part[i] = 0.f;
 #pragma unroll
         for (int h = 0; h < 32; ++h) {
-          s0 = fmaf(wreg[h], fmaxf(__uint_as_float(r0[h]), 0.f), s0);
-          s1 = fmaf(wreg[32 + h], fmaxf(__uint_as_float(r1[h]), 0.f), s1);
+          part[h & 3] = fmaf(wreg[h], fmaxf(__uint_as_float(r0[h]), 0.f), part[h & 3]);
+          part[4 + (h & 3)] = fmaf(wreg[32 + h], fmaxf(__uint_as_float(r1[h]), 0.f), part[4 + (h & 3)]);
         }
+        const float total = ((part[0] + part[1]) + (part[2] + part[3])) +
+                            ((part[4] + part[5]) + (part[6] + part[7]));
         const int t = j * kTcTile + rowi;
-        if (t < len) scores[(size_t)b * score_stride + t] = (s0 + s1) * sc;
+        if (t < len) scores[(size_t)b * score_stride + t] = total * sc;
         if (++stage == kTcStages) { stage = 0; phase ^= 1; }
         if (++acc == kTcAcc) { acc = 0; aphase ^= 1; }
       }

@@ -56,7 +56,7 @@ struct AtShared {
   float red[4][kHeads];
   int go[2][2];
   uint64_t kv_full[2], kv_empty[2], q_full[2], q_empty[2];
-  uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_ready, o_free;
+  uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_free;
   uint32_t tmem_base;
   volatile int abort_flag;
   int is_last;
@@ -205,7 +205,6 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
         ptx::mbar_init(smem_u32(&sh.p_full[i]), 4);
         ptx::mbar_init(smem_u32(&sh.p_empty[i]), 1);
       }
-      ptx::mbar_init(smem_u32(&sh.o_ready), 1);
       ptx::mbar_init(smem_u32(&sh.o_free), 4);
       sh.abort_flag = 0;
       ptx::fence_barrier_init();
@@ -286,7 +285,10 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
               l_part[h] *= corr[h];
             }
             if (seg_live > 0) {
-              if (!group_wait(sh, 0, toggle, leader, smem_u32(&sh.o_ready), (n - 1) & 1, 1, status)) break;
+              // PV #(n-1) is complete when P buffer (n-1)&1 has been released for the ((n-1)>>1)-th
+              // time; every phase of that barrier is observed in order, which a parity wait needs.
+              if (!group_wait(sh, 0, toggle, leader, smem_u32(&sh.p_empty[(n - 1) & 1]),
+                              ((n - 1) >> 1) & 1, 1, status)) break;
               ptx::tc_fence_after();
 #pragma unroll
               for (int c = 0; c < 4; ++c) {
@@ -323,7 +325,8 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
         if (j == tpt - 1 || w == w1 - 1) {
           // ------------------ end of this CTA's segment of token t ------------------
           if (seg_live > 0) {
-            if (!group_wait(sh, 0, toggle, leader, smem_u32(&sh.o_ready), (n - 1) & 1, 1, status)) break;
+            if (!group_wait(sh, 0, toggle, leader, smem_u32(&sh.p_empty[(n - 1) & 1]),
+                            ((n - 1) >> 1) & 1, 1, status)) break;
             ptx::tc_fence_after();
           }
 #pragma unroll
@@ -425,7 +428,6 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
           }
           ptx::tc_commit(smem_u32(&sh.kv_empty[pend_stage]));
           ptx::tc_commit(smem_u32(&sh.p_empty[pbuf]));
-          ptx::tc_commit(smem_u32(&sh.o_ready));
           ++np;
           pend = false;
         };

@@ -1,25 +1,37 @@
 // Top-2048 selection over one fp32 score row per request, fused with the page -> global slot
 // remap and the -1 padding (reference: torch.topk + remap, indexer_baseline.py:60, :82-90).
 //
-// One CTA per request.  Scores are mapped to order-preserving 32-bit keys; an 11+11+10 bit
-// most-significant-digit radix descent over shared-memory histograms finds the exact key T of the
-// 2048-th largest score and how many elements equal to T must be taken; a last sweep emits every
-// element above T (warp-aggregated slot allocation) and the required number of elements equal to T
-// (lowest positions first, so the selected SET is deterministic).  The row is staged in shared
-// memory when it fits (<= 49152 scores), otherwise each sweep streams it from L2/global.
+// One CTA (1024 threads) per request; the row is staged in shared memory when it fits (<= 49152
+// scores), otherwise every sweep streams it from L2/global.
+//
+// Fast path (three sweeps): (A) min and max of the row; (B) a 2048-bin histogram over the LINEAR
+// map of [min,max] -- scores of one request are spread over hundreds of bins, so shared-memory
+// atomics rarely collide, unlike a histogram of the leading float bits where a few exponent bins
+// take everything; (C) every element in a bin above the boundary bin is emitted (warp-aggregated
+// slot allocation), the few elements inside the boundary bin become candidates.  The linear map
+// is monotone, so the bins order the elements exactly; the candidates are then ranked exactly by
+// (order-preserving 32-bit key, lower position first) and the missing number of them is emitted.
+// Fallback: when the boundary bin holds more than 1024 elements (flat or degenerate rows, massive
+// ties) an 11+11+10 bit radix descent restricted to that bin finds the exact threshold key.
+// The selected SET is deterministic; the order inside the output row is not part of the contract.
 // Nothing here waits on another CTA.
 #include "common.cuh"
 
 namespace dsa {
 
 constexpr int kSelThreads = 1024;
-constexpr int kSelRowCap = 49152;  // keys staged in dynamic shared memory (192 KB)
+constexpr int kSelRowCap = 49152;  // scores staged in dynamic shared memory (192 KB)
 constexpr int kSelBins = 2048;
+constexpr int kSelCandCap = 1024;
+constexpr float kSelFloor = -3.0e38f;  // -inf / NaN scores are ranked as this value
 
 struct SelShared {
   uint32_t hist[kSelBins];
+  uint32_t cand_key[kSelCandCap];
+  int cand_idx[kSelCandCap];
   uint32_t warp_sums[32];
-  uint32_t digit, above, ties, cnt_gt, cnt_eq;
+  uint32_t red_a[32], red_b[32];
+  uint32_t digit, above, ties, cnt_gt, cnt_gt2, cnt_eq, cnt_cand, kmin, kmax;
 };
 
 // Inclusive prefix sum over the CTA in thread order.
@@ -47,39 +59,153 @@ __device__ __forceinline__ uint32_t block_inclusive_scan(uint32_t v, uint32_t* w
   return v;
 }
 
+// Find the digit d (bins are scanned from the top) such that count(bins > d) < k <= count(bins >= d).
+// Thread t owns bins nb-1-per*t ... downwards.  Results in sh.digit / sh.above / sh.ties.
+__device__ __forceinline__ void find_boundary_bin(SelShared& sh, uint32_t nb, uint32_t k) {
+  const int tid = threadIdx.x;
+  const int per = nb / kSelThreads;  // 2 or 1
+  uint32_t c_hi = sh.hist[nb - 1 - per * tid];
+  uint32_t c_lo = per == 2 ? sh.hist[nb - 2 - per * tid] : 0u;
+  uint32_t incl = block_inclusive_scan(c_hi + c_lo, sh.warp_sums);
+  uint32_t excl = incl - (c_hi + c_lo);
+  if (excl < k && k <= incl) {
+    if (excl + c_hi >= k) {
+      sh.digit = nb - 1 - per * tid; sh.above = excl; sh.ties = c_hi;
+    } else {
+      sh.digit = nb - 2 - per * tid; sh.above = excl + c_hi; sh.ties = c_lo;
+    }
+  }
+  __syncthreads();
+}
+
 __global__ void __launch_bounds__(kSelThreads, 1)
 topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
                    const int32_t* __restrict__ seq_lens, const int32_t* __restrict__ block_table,
                    int64_t bt_stride, int32_t* __restrict__ out, int64_t out_stride, int max_pages,
                    int32_t* status) {
-  extern __shared__ uint32_t row_keys[];
+  extern __shared__ float row_s[];
   __shared__ SelShared sh;
 
   const int b = blockIdx.x;
   const int tid = threadIdx.x;
-  const int lane = tid & 31;
+  const int lane = tid & 31, warp = tid >> 5;
   int len = seq_lens[b];
   len = max(0, min(len, max_pages * kPage));
   int32_t* out_row = out + (size_t)b * out_stride;
   const int32_t* table = block_table + (size_t)b * bt_stride;
   const float* row = scores + (size_t)b * score_stride;
+  auto slot_of = [&](int i) -> int32_t { return table[i >> 6] * kPage + (i & 63); };
 
   if (len <= kTopK) {  // every token is selected: no scores needed
-    for (int i = tid; i < kTopK; i += kSelThreads)
-      out_row[i] = i < len ? table[i >> 6] * kPage + (i & 63) : -1;
+    for (int i = tid; i < kTopK; i += kSelThreads) out_row[i] = i < len ? slot_of(i) : -1;
     return;
   }
 
   const bool staged = len <= kSelRowCap;
-  if (staged) {
-    for (int i = tid; i < len; i += kSelThreads) row_keys[i] = float_to_ordered(row[i]);
+  auto value_at = [&](int i) -> float { return staged ? row_s[i] : __ldg(row + i); };
+
+  // ---- sweep A: stage the row, min / max ------------------------------------------------------
+  {
+    float mn = INFINITY, mx = kSelFloor;
+    for (int i = tid; i < len; i += kSelThreads) {
+      float v = __ldg(row + i);
+      if (staged) row_s[i] = v;
+      v = fmaxf(v, kSelFloor);
+      mn = fminf(mn, v);
+      mx = fmaxf(mx, v);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    if (lane == 0) { sh.red_a[warp] = __float_as_uint(mn); sh.red_b[warp] = __float_as_uint(mx); }
+    for (int i = tid; i < kSelBins; i += kSelThreads) sh.hist[i] = 0;
+    if (tid == 0) { sh.cnt_gt = 0; sh.cnt_gt2 = 0; sh.cnt_eq = 0; sh.cnt_cand = 0; }
+    __syncthreads();
+    if (warp == 0) {
+      mn = __uint_as_float(sh.red_a[lane]);
+      mx = __uint_as_float(sh.red_b[lane]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      }
+      if (lane == 0) { sh.kmin = __float_as_uint(mn); sh.kmax = __float_as_uint(mx); }
+    }
+    __syncthreads();
   }
-  if (tid == 0) { sh.cnt_gt = 0; sh.cnt_eq = 0; }
-  auto key_at = [&](int i) -> uint32_t {
-    return staged ? row_keys[i] : float_to_ordered(__ldg(row + i));
+  const float lo = __uint_as_float(sh.kmin);
+  const float span = __uint_as_float(sh.kmax) - lo;
+  const float inv = span > 0.f ? (float)kSelBins / span : 0.f;
+  auto bin_of = [&](float v) -> int {
+    return min(kSelBins - 1, __float2int_rz((fmaxf(v, kSelFloor) - lo) * inv));
   };
 
-  uint32_t prefix = 0, mask = 0, k_rem = kTopK;
+  // ---- sweep B: histogram of the linear bins ---------------------------------------------------
+  for (int i = tid; i < len; i += kSelThreads) atomicAdd(&sh.hist[bin_of(value_at(i))], 1u);
+  __syncthreads();
+  find_boundary_bin(sh, kSelBins, kTopK);
+  const int edge = (int)sh.digit;          // boundary bin
+  const uint32_t above = sh.above;         // elements in higher bins: all selected
+  const uint32_t in_edge = sh.ties;        // elements in the boundary bin
+  const uint32_t need = kTopK - above;     // how many of them are selected (>= 1)
+  const bool few = in_edge <= (uint32_t)kSelCandCap;
+  __syncthreads();
+
+  // ---- sweep C: emit everything above the boundary bin, collect the boundary bin ---------------
+  const int sweeps = (len + kSelThreads - 1) / kSelThreads;
+  for (int s = 0; s < sweeps; ++s) {
+    const int i = s * kSelThreads + tid;
+    float v = 0.f;
+    int bin = -1;
+    if (i < len) { v = value_at(i); bin = bin_of(v); }
+    const bool gt = bin > edge;
+    const uint32_t m = __ballot_sync(0xffffffffu, gt);
+    if (m) {
+      uint32_t base = 0;
+      if (lane == 0) base = atomicAdd(&sh.cnt_gt, __popc(m));
+      base = __shfl_sync(0xffffffffu, base, 0);
+      if (gt) {
+        const uint32_t pos = base + __popc(m & ((1u << lane) - 1));
+        if (pos < (uint32_t)kTopK) out_row[pos] = slot_of(i);
+      }
+    }
+    if (few && bin == edge) {
+      const uint32_t c = atomicAdd(&sh.cnt_cand, 1u);
+      if (c < (uint32_t)kSelCandCap) { sh.cand_key[c] = float_to_ordered(v); sh.cand_idx[c] = i; }
+    }
+  }
+  __syncthreads();
+
+  if (few) {
+    // ---- exact ranking of the candidates: higher key first, lower position first on ties -------
+    const uint32_t n = min(sh.cnt_cand, (uint32_t)kSelCandCap);
+    if (tid < (int)n) {
+      const uint32_t ka = sh.cand_key[tid];
+      const int ia = sh.cand_idx[tid];
+      uint32_t rank = 0;
+      if (n != need) {
+        for (uint32_t j = 0; j < n; ++j) {
+          const uint32_t kb = sh.cand_key[j];
+          rank += (kb > ka) || (kb == ka && sh.cand_idx[j] < ia);
+        }
+      } else {
+        rank = tid;
+      }
+      if (rank < need) out_row[above + rank] = slot_of(ia);
+    }
+    if (tid == 0 && (sh.cnt_gt != above || n != in_edge)) raise_status(status, DSA_STATUS_TOPK_COUNT);
+    return;
+  }
+
+  // ---- fallback: radix descent over the ordered keys of the boundary bin ------------------------
+  auto key_in_edge = [&](int i, uint32_t& key) -> bool {
+    const float v = value_at(i);
+    key = float_to_ordered(v);
+    return bin_of(v) == edge;
+  };
+  uint32_t prefix = 0, mask = 0, k_rem = need;
 #pragma unroll 1
   for (int pass = 0; pass < 3; ++pass) {
     const int shift = pass == 0 ? 21 : (pass == 1 ? 10 : 0);
@@ -88,65 +214,50 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
     for (int i = tid; i < kSelBins; i += kSelThreads) sh.hist[i] = 0;
     __syncthreads();
     for (int i = tid; i < len; i += kSelThreads) {
-      uint32_t k = key_at(i);
-      if ((k & mask) == prefix) atomicAdd(&sh.hist[(k >> shift) & (nb - 1)], 1u);
+      uint32_t k;
+      if (key_in_edge(i, k) && (k & mask) == prefix) atomicAdd(&sh.hist[(k >> shift) & (nb - 1)], 1u);
     }
     __syncthreads();
-    // Thread t owns the bins nb-1-per*t ... (descending), so a prefix scan in thread order is a
-    // suffix sum over digits.
-    const int per = nb / kSelThreads;  // 2 or 1
-    uint32_t c_hi = sh.hist[nb - 1 - per * tid];
-    uint32_t c_lo = per == 2 ? sh.hist[nb - 2 - per * tid] : 0u;
-    uint32_t incl = block_inclusive_scan(c_hi + c_lo, sh.warp_sums);
-    uint32_t excl = incl - (c_hi + c_lo);
-    if (excl < k_rem && k_rem <= incl) {
-      if (excl + c_hi >= k_rem) {
-        sh.digit = nb - 1 - per * tid; sh.above = excl; sh.ties = c_hi;
-      } else {
-        sh.digit = nb - 2 - per * tid; sh.above = excl + c_hi; sh.ties = c_lo;
-      }
-    }
-    __syncthreads();
+    find_boundary_bin(sh, nb, k_rem);
     prefix |= sh.digit << shift;
     mask |= (nb - 1) << shift;
     k_rem -= sh.above;
     __syncthreads();
   }
-  const uint32_t thresh = prefix;         // key of the 2048-th largest score
-  const uint32_t n_gt = kTopK - k_rem;    // elements strictly above it
-  const uint32_t ties = sh.ties;          // elements equal to it (>= k_rem)
-  const bool take_all_ties = ties == k_rem;
-
-  const int sweeps = (len + kSelThreads - 1) / kSelThreads;
+  const uint32_t thresh = prefix;             // key of the last selected element
+  const uint32_t n_gt = need - k_rem;         // boundary-bin elements strictly above it
+  const bool take_all_ties = sh.ties == k_rem;
   for (int s = 0; s < sweeps; ++s) {
     const int i = s * kSelThreads + tid;
-    uint32_t k = i < len ? key_at(i) : 0u;
-    const bool gt = i < len && k > thresh;
-    const bool eq = i < len && k == thresh;
-    uint32_t m = __ballot_sync(0xffffffffu, gt);
+    uint32_t k = 0;
+    const bool in = i < len && key_in_edge(i, k);
+    const bool gt = in && k > thresh;
+    const bool eq = in && k == thresh;
+    const uint32_t m = __ballot_sync(0xffffffffu, gt);
     if (m) {
       uint32_t base = 0;
-      if (lane == 0) base = atomicAdd(&sh.cnt_gt, __popc(m));
+      if (lane == 0) base = atomicAdd(&sh.cnt_gt2, __popc(m));
       base = __shfl_sync(0xffffffffu, base, 0);
       if (gt) {
-        uint32_t pos = base + __popc(m & ((1u << lane) - 1));
-        if (pos < kTopK) out_row[pos] = table[i >> 6] * kPage + (i & 63);
+        const uint32_t pos = above + base + __popc(m & ((1u << lane) - 1));
+        if (pos < (uint32_t)kTopK) out_row[pos] = slot_of(i);
       }
     }
     if (take_all_ties && eq) {
-      uint32_t pos = n_gt + atomicAdd(&sh.cnt_eq, 1u);
-      if (pos < kTopK) out_row[pos] = table[i >> 6] * kPage + (i & 63);
+      const uint32_t pos = above + n_gt + atomicAdd(&sh.cnt_eq, 1u);
+      if (pos < (uint32_t)kTopK) out_row[pos] = slot_of(i);
     }
   }
   if (!take_all_ties) {
-    // More elements tie with the threshold than are needed: keep the lowest positions.
+    // more elements equal the threshold than are needed: keep the lowest positions
     uint32_t running = 0;
     for (int s = 0; s < sweeps && running < k_rem; ++s) {
       const int i = s * kSelThreads + tid;
-      const bool eq = i < len && key_at(i) == thresh;
-      uint32_t incl = block_inclusive_scan(eq ? 1u : 0u, sh.warp_sums);
-      uint32_t rank = running + incl - 1;
-      if (eq && rank < k_rem) out_row[n_gt + rank] = table[i >> 6] * kPage + (i & 63);
+      uint32_t k = 0;
+      const bool eq = i < len && key_in_edge(i, k) && k == thresh;
+      const uint32_t incl = block_inclusive_scan(eq ? 1u : 0u, sh.warp_sums);
+      const uint32_t rank = running + incl - 1;
+      if (eq && rank < k_rem) out_row[above + n_gt + rank] = slot_of(i);
       if (tid == kSelThreads - 1) sh.above = incl;
       __syncthreads();
       running += sh.above;
@@ -154,18 +265,22 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
     }
   }
   __syncthreads();
-  if (tid == 0 && sh.cnt_gt != n_gt) raise_status(status, DSA_STATUS_TOPK_COUNT);
+  if (tid == 0 && (sh.cnt_gt != above || sh.cnt_gt2 != n_gt)) raise_status(status, DSA_STATUS_TOPK_COUNT);
 }
 
 cudaError_t launch_topk_select(const float* scores, int64_t score_stride, const int32_t* seq_lens,
                                const int32_t* block_table, int64_t bt_stride, int32_t* out,
                                int64_t out_stride, int batch, int max_pages, int32_t* status,
                                cudaStream_t stream) {
-  size_t smem = sizeof(uint32_t) * (size_t)min(kSelRowCap, max(max_pages * kPage, 1));
-  cudaError_t e = cudaFuncSetAttribute(topk_select_kernel,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)(sizeof(uint32_t) * kSelRowCap));
-  if (e != cudaSuccess) return e;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(topk_select_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)(sizeof(float) * kSelRowCap));
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  size_t smem = sizeof(float) * (size_t)min(kSelRowCap, max(max_pages * kPage, 1));
   topk_select_kernel<<<batch, kSelThreads, smem, stream>>>(scores, score_stride, seq_lens,
                                                            block_table, bt_stride, out, out_stride,
                                                            max_pages, status);
