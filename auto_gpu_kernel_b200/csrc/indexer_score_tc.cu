@@ -10,27 +10,32 @@
 //   warp 0  producer : walks its share of (request, 128-token tile) work items, looks the two pages
 //                      of a tile up in block_table (32 tiles per coalesced lookup) and issues, per
 //                      page, one 2-D TMA box (64 rows x 128 B, 128-byte swizzle) for the keys and one
-//                      256-byte bulk copy for the fp32 scales, into an 8-deep shared-memory ring;
+//                      256-byte bulk copy for the fp32 scales, into a 4-deep shared-memory ring;
 //   warp 1  MMA      : per tile 4 x tcgen05.mma M=128 (tokens) x N=64 (heads) x K=32, A = key tile,
 //                      B = the request's q (both K-major in shared memory), D in one of 4 TMEM
 //                      accumulator slots; tcgen05.commit releases the ring slot and publishes D;
 //   warps 2-5 epilogue: tcgen05.ld of the token's 64 head sums, relu, dot with w, times the token
 //                      scale, one coalesced fp32 store per token.
 //
+// Two such CTAs run per SM (each uses half of the shared memory, registers and TMEM): the three
+// roles are strictly serial instruction streams, and at 64 accumulator columns per tile their issue
+// latency, not the tensor pipe, bounds one pipeline, so two independent pipelines per SM are needed
+// to keep the HBM stream saturated.
 // Work is split evenly in tiles (not requests) across CTAs using an in-kernel prefix sum of the
 // device-resident seq_lens, so ragged batches balance without a host synchronisation.
 // Every mbarrier wait is time-bounded; on expiry the CTA records DSA_STATUS_WAIT_TIMEOUT, lets
 // copies in flight land, frees its TMEM and returns.
 #include "common.cuh"
 #include "ptx.cuh"
+#include "tmap.cuh"
 
 namespace dsa {
 
-constexpr int kTcStages = 8;
+constexpr int kTcStages = 4;
 constexpr int kTcAcc = 4;
 constexpr int kTcTile = 128;
 constexpr int kTcThreads = 192;
-constexpr int kTcMaxBatch = 4096;
+constexpr int kTcMaxBatch = 2048;
 constexpr int kTcTmemCols = 256;            // 4 accumulators x 64 fp32 columns
 constexpr int kTileDataBytes = 2 * kPageDataBytes;  // 16384
 constexpr uint32_t kIdescF8 = ptx::idesc(ptx::kFmtE4M3, ptx::kFmtE4M3, false, false, 128, 64);
@@ -66,7 +71,7 @@ __device__ __forceinline__ int locate(const int* prefix, int batch, int w) {
   return lo;
 }
 
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kTcThreads, 2)
 indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
                         const __grid_constant__ CUtensorMap tmap_q,
                         const uint8_t* __restrict__ k_cache, const float* __restrict__ weights,
@@ -193,25 +198,26 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
       // ======================= MMA issuer =======================
       if (lane == 0) {
         int stage = 0, phase = 0, qslot = 0, qphase = 0, acc = 0, aphase = 0;
-        int b = locate(sh.prefix, batch, w0), cur_b = -1;
-        for (int w = w0; w < w1 && !sh.abort_flag; ++w) {
-          while (sh.prefix[b + 1] <= w) ++b;
-          if (b != cur_b) {
-            if (cur_b >= 0) {  // all MMAs reading the previous q are issued: free it on completion
-              ptx::tc_commit(smem_u32(&sh.qempty[qslot ^ 1]));
-            }
+        int b = locate(sh.prefix, batch, w0), next_change = w0;
+        uint32_t qbase = q_addr;
+        // descriptor bits that never change: LBO = 16 B, SBO = 1024 B, version 1, 128-byte swizzle
+        const uint64_t desc_hi = ptx::smem_desc_sw128(0, 16, 1024);
+        for (int w = w0; w < w1; ++w) {
+          if (w >= next_change) {  // first tile of a request
+            if (w > w0) ptx::tc_commit(smem_u32(&sh.qempty[qslot ^ 1]));  // previous q: free when read
+            while (sh.prefix[b + 1] <= w) ++b;
+            next_change = sh.prefix[b + 1];
             DSA_WAIT(sh.qfull[qslot], qphase);
-            cur_b = b;
+            qbase = q_addr + qslot * kPageDataBytes;
             qslot ^= 1;
             if (qslot == 0) qphase ^= 1;
           }
-          const uint32_t qbase = q_addr + (qslot ^ 1) * kPageDataBytes;
           DSA_WAIT(sh.accempty[acc], aphase ^ 1);
           DSA_WAIT(sh.full[stage], phase);
           if (sh.abort_flag) break;
           ptx::tc_fence_after();
-          const uint64_t adesc = ptx::smem_desc_sw128(data_addr + stage * kTileDataBytes, 16, 1024);
-          const uint64_t bdesc = ptx::smem_desc_sw128(qbase, 16, 1024);
+          const uint64_t adesc = desc_hi | (uint64_t)((data_addr + stage * kTileDataBytes) >> 4);
+          const uint64_t bdesc = desc_hi | (uint64_t)(qbase >> 4);
           const uint32_t d = tmem_base + acc * kIdxHeads;
 #pragma unroll
           for (int k = 0; k < 4; ++k)  // K = 32 fp8 = 32 bytes per instruction -> +2 in 16 B units
@@ -228,11 +234,13 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
       const int quarter = warp & 3;
       const int rowi = quarter * 32 + lane;
       int stage = 0, phase = 0, acc = 0, aphase = 0;
-      int b = locate(sh.prefix, batch, w0), cur_b = -1, len = 0;
+      int b = locate(sh.prefix, batch, w0), next_change = w0, first_tile = 0, len = 0;
       float wreg[kIdxHeads];
-      for (int w = w0; w < w1 && !sh.abort_flag; ++w) {
-        while (sh.prefix[b + 1] <= w) ++b;
-        if (b != cur_b) {
+      for (int w = w0; w < w1; ++w) {
+        if (w >= next_change) {
+          while (sh.prefix[b + 1] <= w) ++b;
+          next_change = sh.prefix[b + 1];
+          first_tile = sh.prefix[b];
           const float4* wp = reinterpret_cast<const float4*>(weights + (size_t)b * kIdxHeads);
 #pragma unroll
           for (int i = 0; i < kIdxHeads / 4; ++i) {
@@ -240,38 +248,33 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
             wreg[4 * i] = v.x; wreg[4 * i + 1] = v.y; wreg[4 * i + 2] = v.z; wreg[4 * i + 3] = v.w;
           }
           len = max(0, min(seq_lens[b], max_pages * kPage));
-          cur_b = b;
         }
-        const int j = w - sh.prefix[b];
         DSA_WAIT(sh.full[stage], phase);
         const float sc = sh.scale[stage][rowi];
         DSA_WAIT(sh.accfull[acc], aphase);
         if (sh.abort_flag) break;
         ptx::tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kIdxHeads;
-        uint32_t r0[32], r1[32];
-        ptx::tmem_ld32(taddr, r0);
-        ptx::tmem_ld32(taddr + 32, r1);
-        ptx::tmem_wait_ld();
+        // four 16-column chunks keep the live register set small enough for two CTAs per SM;
+        // four independent partial sums keep the FMA chains short
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[16];
+          ptx::tmem_ld16(taddr + c * 16, r);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int h = 0; h < 16; ++h)
+            part[h & 3] = fmaf(wreg[c * 16 + h], fmaxf(__uint_as_float(r[h]), 0.f), part[h & 3]);
+        }
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) {
           ptx::mbar_arrive(smem_u32(&sh.accempty[acc]));
           ptx::mbar_arrive(smem_u32(&sh.empty[stage]));
         }
-        // eight independent partial sums: the FMA chain per sum is 8 long instead of 64
-        float part[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) part[i] = 0.f;
-#pragma unroll
-        for (int h = 0; h < 32; ++h) {
-          part[h & 3] = fmaf(wreg[h], fmaxf(__uint_as_float(r0[h]), 0.f), part[h & 3]);
-          part[4 + (h & 3)] = fmaf(wreg[32 + h], fmaxf(__uint_as_float(r1[h]), 0.f), part[4 + (h & 3)]);
-        }
-        const float total = ((part[0] + part[1]) + (part[2] + part[3])) +
-                            ((part[4] + part[5]) + (part[6] + part[7]));
-        const int t = j * kTcTile + rowi;
-        if (t < len) scores[(size_t)b * score_stride + t] = total * sc;
+        const int t = (w - first_tile) * kTcTile + rowi;
+        if (t < len) scores[(size_t)b * score_stride + t] = ((part[0] + part[1]) + (part[2] + part[3])) * sc;
         if (++stage == kTcStages) { stage = 0; phase ^= 1; }
         if (++acc == kTcAcc) { acc = 0; aphase ^= 1; }
       }
@@ -291,45 +294,9 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
 }
 
 // ------------------------------------------------------------------------------------------ host
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// rows x 128 bytes, box = 64 rows x 128 bytes, 128-byte swizzle
 static bool make_rows128_map(CUtensorMap* map, const void* base, uint64_t rows) {
-  EncodeTiledFn enc = encode_tiled_fn();
-  if (enc == nullptr) return false;
-  cuuint64_t dims[2] = {128, rows};
-  cuuint64_t strides[1] = {128};
-  cuuint32_t box[2] = {128, 64};
-  cuuint32_t estr[2] = {1, 1};
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
-             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-static int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
+  // rows x 128 bytes, box = 64 rows x 128 bytes, 128-byte swizzle
+  return make_tmap_2d_sw128(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, base, 128, rows, 128, 64);
 }
 
 cudaError_t launch_indexer_score_tc(const void* q_fp8, const void* k_cache, const float* weights,
@@ -352,7 +319,7 @@ cudaError_t launch_indexer_score_tc(const void* q_fp8, const void* k_cache, cons
     CUtensorMap tmap_q;
     const uint8_t* qp = static_cast<const uint8_t*>(q_fp8) + (size_t)b0 * kIdxHeads * kIdxDim;
     if (!make_rows128_map(&tmap_q, qp, (uint64_t)nb * kIdxHeads)) return cudaErrorInvalidValue;
-    indexer_score_tc_kernel<<<sm_count(), kTcThreads, kTcDynBytes, stream>>>(
+    indexer_score_tc_kernel<<<2 * sm_count(), kTcThreads, kTcDynBytes, stream>>>(
         tmap_k, tmap_q, static_cast<const uint8_t*>(k_cache), weights + (size_t)b0 * kIdxHeads,
         seq_lens + b0, block_table + (size_t)b0 * bt_stride, bt_stride,
         scores + (size_t)b0 * score_stride, score_stride, nb, num_pages, max_pages, skip_short,

@@ -63,6 +63,18 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, 
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
+// Gather of four rows of a 2-D tensor (row indices r0..r3, columns starting at x) into four
+// consecutive 128-byte rows of shared memory; the tensor map's box is {64 elements, 1 row}.  Rows
+// outside the tensor (e.g. index -1) are filled with zeros.  No multicast.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* m, int32_t x, int32_t r0,
+                                            int32_t r1, int32_t r2, int32_t r3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3),
+        "r"(bar)
+      : "memory");
+}
 // 1-D bulk copy global -> shared; src/dst 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes,
                                              uint32_t bar) {

@@ -23,14 +23,21 @@
 // CTA's range covers parts ("segments") of at most a few tokens; a token covered by several CTAs is
 // merged by whichever of them finishes last (atomic arrival counter, nobody waits).
 //
-// Warp roles (288 threads): warps 0-3 softmax + epilogue (TMEM lane quarter = warp), warp 4 MMA
-// issuer, warps 5-8 gather producers (cp.async 16 B with zero-fill for masked rows, two stages).
+// Warp roles (192 threads): warps 0-3 softmax + epilogue (TMEM lane quarter = warp), warp 4 MMA
+// issuer, warp 5 gather producer.  The gather uses the TMA tile::gather4 mode: one instruction
+// fetches a 128-byte column block of four arbitrary rows of the flat cache into four consecutive
+// swizzled shared-memory rows (144 instructions per 64-row tile, spread over the 32 lanes); rows
+// with index -1 are out of the tensor and arrive as zeros.  Two stages.
+// Consecutive tcgen05.mma into one accumulator serialise on its latency at N = 16, so S^T is
+// accumulated in four partial accumulators used round-robin (summed after tcgen05.ld) and the PV
+// products are issued k-step-major across the four 128-row output chunks.
 // The running max is only refreshed (and O rescaled in TMEM) when a logit exceeds it by more than
 // 2^8, so the common tile costs one exp2 per logit and no cross-thread reduction; row sums stay
 // per-thread until the end of the segment.  All waits are time-bounded; group decisions are taken
 // by one thread and broadcast, so a timeout makes every role leave together.
 #include "common.cuh"
 #include "ptx.cuh"
+#include "tmap.cuh"
 
 namespace dsa {
 
@@ -40,9 +47,9 @@ constexpr int kAtStageBytes = 9 * kAtBlockBytes;   // 73728
 constexpr int kAtQBlockBytes = kHeads * 128;       // 2048
 constexpr int kAtQBytes = 9 * kAtQBlockBytes;      // 18432
 constexpr int kAtPBytes = kHeads * 128;            // 2048
-constexpr int kAtThreads = 288;
-constexpr int kAtTmemCols = 128;
-constexpr int kAtSCol = 64;                        // S^T buffers at columns 64 and 96; O^T at 0..63
+constexpr int kAtThreads = 192;
+constexpr int kAtTmemCols = 256;
+constexpr int kAtSCol = 64;                        // O^T at 0..63; S^T buffer b at 64+64b (4 partials x 16)
 constexpr float kAtLog2e = 1.4426950408889634f;
 constexpr float kAtRescaleGap = 8.f;
 constexpr uint32_t kIdescQK = ptx::idesc(ptx::kFmtBF16, ptx::kFmtBF16, false, false, 64, 16);
@@ -50,11 +57,10 @@ constexpr uint32_t kIdescPV = ptx::idesc(ptx::kFmtBF16, ptx::kFmtBF16, true, fal
 
 struct AtShared {
   int idx[2][kAtTile];
-  int any_live[2][4];
   int live[2];
   int need[4];
   float red[4][kHeads];
-  int go[2][2];
+  int go[1][2];
   uint64_t kv_full[2], kv_empty[2], q_full[2], q_empty[2];
   uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_free;
   uint32_t tmem_base;
@@ -173,8 +179,9 @@ __device__ void at_merge_segments(const AtPartials& w, int t, int n_seg, int seg
 }
 
 __global__ void __launch_bounds__(kAtThreads, 1)
-sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloat16* __restrict__ q_pe,
-                      const __nv_bfloat16* __restrict__ ckv, const __nv_bfloat16* __restrict__ kpe,
+sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_ckv,
+                      const __grid_constant__ CUtensorMap tmap_kpe,
+                      const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloat16* __restrict__ q_pe,
                       const int32_t* __restrict__ indices, int64_t index_stride, float scale_log2,
                       __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int tokens, int topk,
                       int64_t num_slots, AtPlan plan, void* ws_raw, int32_t* status) {
@@ -196,9 +203,9 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
   if (warp == 4) {
     if (lane == 0) {
       for (int i = 0; i < 2; ++i) {
-        ptx::mbar_init(smem_u32(&sh.kv_full[i]), 128 + 1);
+        ptx::mbar_init(smem_u32(&sh.kv_full[i]), 1);
         ptx::mbar_init(smem_u32(&sh.kv_empty[i]), 2);
-        ptx::mbar_init(smem_u32(&sh.q_full[i]), 128);
+        ptx::mbar_init(smem_u32(&sh.q_full[i]), 32);
         ptx::mbar_init(smem_u32(&sh.q_empty[i]), 1);
         ptx::mbar_init(smem_u32(&sh.s_full[i]), 1);
         ptx::mbar_init(smem_u32(&sh.s_empty[i]), 4);
@@ -208,6 +215,8 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
       ptx::mbar_init(smem_u32(&sh.o_free), 4);
       sh.abort_flag = 0;
       ptx::fence_barrier_init();
+      ptx::prefetch_tensormap(&tmap_ckv);
+      ptx::prefetch_tensormap(&tmap_kpe);
     }
     __syncwarp();
     ptx::tmem_alloc(smem_u32(&sh.tmem_base), kAtTmemCols);
@@ -249,10 +258,18 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
           const int sbuf = n & 1, sphase = (n >> 1) & 1;
           if (!group_wait(sh, 0, toggle, leader, smem_u32(&sh.s_full[sbuf]), sphase, 1, status)) break;
           ptx::tc_fence_after();
-          uint32_t sr[16];
-          ptx::tmem_ld16(tmem_base + lane_base + kAtSCol + sbuf * 32, sr);
+          uint32_t sr[16], sp1[16], sp2[16], sp3[16];
+          const uint32_t s_addr = tmem_base + lane_base + kAtSCol + sbuf * 64;
+          ptx::tmem_ld16(s_addr, sr);
+          ptx::tmem_ld16(s_addr + 16, sp1);
+          ptx::tmem_ld16(s_addr + 32, sp2);
+          ptx::tmem_ld16(s_addr + 48, sp3);
           ptx::tmem_wait_ld();
           ptx::tc_fence_before();
+#pragma unroll
+          for (int h = 0; h < kHeads; ++h)
+            sr[h] = __float_as_uint((__uint_as_float(sr[h]) + __uint_as_float(sp1[h])) +
+                                    (__uint_as_float(sp2[h]) + __uint_as_float(sp3[h])));
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(smem_u32(&sh.s_empty[sbuf]));
           float x[kHeads];
@@ -418,9 +435,9 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
           const uint32_t a0 = kv_addr + pend_stage * kAtStageBytes;
           const uint32_t b0 = p_addr + pbuf * kAtPBytes;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int ks = 0; ks < 4; ++ks) {
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
+            for (int c = 0; c < 4; ++c) {
               const uint64_t ad = ptx::smem_desc_sw128(a0 + 2 * c * kAtBlockBytes + ks * 2048, kAtBlockBytes, 1024);
               const uint64_t bd = ptx::smem_desc_sw128(b0 + ks * 32, 16, 1024);
               ptx::mma_bf16(tmem_base + c * 16, ad, bd, kIdescPV, !(pend_first && ks == 0));
@@ -463,7 +480,7 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
               for (int k = 0; k < 4; ++k) {
                 const uint64_t ad = ptx::smem_desc_sw128(a0 + kb * kAtBlockBytes + k * 32, 16, 1024);
                 const uint64_t bd = ptx::smem_desc_sw128(b0 + kb * kAtQBlockBytes + k * 32, 16, 1024);
-                ptx::mma_bf16(tmem_base + kAtSCol + sbuf * 32, ad, bd, kIdescQK, (kb | k) != 0);
+                ptx::mma_bf16(tmem_base + kAtSCol + sbuf * 64 + 16 * k, ad, bd, kIdescQK, kb != 0);
               }
             }
             ptx::tc_commit(smem_u32(&sh.s_full[sbuf]));
@@ -484,20 +501,25 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
       }
       __syncwarp();
     } else {
-      // =========================== gather producers ===========================
-      const int ptid = tid - 160, pwarp = ptid >> 5;
-      const bool leader = ptid == 0;
-      int toggle = 0, stage = 0, phase = 0, qb = 0, qphase = 0;
+      // =========================== gather producer (one warp) ===========================
+      int stage = 0, phase = 0, qb = 0, qphase = 0;
       long cur_t = -1;
-      for (long w = w0; w < w1; ++w) {
+      bool ok = true;
+      const int group = lane & 15, half = lane >> 4;  // lane -> rows 4*group..4*group+3, half of the blocks
+      for (long w = w0; w < w1 && ok; ++w) {
         const long t = w / tpt;
         const int j = (int)(w - t * tpt);
         if (t != cur_t) {
-          if (!group_wait(sh, 1, toggle, leader, smem_u32(&sh.q_empty[qb]), qphase ^ 1, 2, status)) break;
+          if (lane == 0) {
+            ok = !sh.abort_flag && ptx::mbar_wait(smem_u32(&sh.q_empty[qb]), qphase ^ 1);
+            if (!ok && !sh.abort_flag) { sh.abort_flag = 1; raise_status(status, DSA_STATUS_WAIT_TIMEOUT); }
+          }
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) break;
           const uint32_t qdst = q_addr + qb * kAtQBytes;
-#pragma unroll
-          for (int it = 0; it < 9; ++it) {
-            const int c = it * 128 + ptid, h = c / 72, jj = c - h * 72;
+#pragma unroll 4
+          for (int it = 0; it < 36; ++it) {
+            const int c = it * 32 + lane, h = c / 72, jj = c - h * 72;
             const __nv_bfloat16* src = jj < 64 ? q_nope + ((size_t)(t * kHeads + h) * kCkv + jj * 8)
                                                : q_pe + ((size_t)(t * kHeads + h) * kKpe + (jj - 64) * 8);
             ptx::cp_async16(qdst + (jj >> 3) * kAtQBlockBytes + h * 128 + (((jj & 7) ^ (h & 7)) << 4), src, 16);
@@ -507,38 +529,48 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
           qb ^= 1;
           if (qb == 0) qphase ^= 1;
         }
-        int my = -1;
-        if (ptid < kAtTile) {
-          const int k = j * kAtTile + ptid;
-          if (k < topk) my = indices[(size_t)t * index_stride + k];
-          if (my >= num_slots) { raise_status(status, DSA_STATUS_BAD_SLOT); my = -1; }
-          if (my < 0) my = -1;
+        // this lane's four row indices (both halves of the warp read the same 16 groups)
+        int r[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int k = j * kAtTile + group * 4 + i;
+          int v = k < topk ? __ldg(indices + (size_t)t * index_stride + k) : -1;
+          if (v >= num_slots) { raise_status(status, DSA_STATUS_BAD_SLOT); v = -1; }
+          r[i] = v < 0 ? -1 : v;
         }
-        if (!group_wait(sh, 1, toggle, leader, smem_u32(&sh.kv_empty[stage]), phase ^ 1, 2, status)) break;
-        if (ptid < kAtTile) sh.idx[stage][ptid] = my;
-        const bool any = __any_sync(0xffffffffu, my >= 0);
-        if (lane == 0) sh.any_live[stage][pwarp] = any;
-        ptx::named_bar_sync(2, 128);
-        const bool live = (sh.any_live[stage][0] | sh.any_live[stage][1]) != 0;
+        const bool live = __any_sync(0xffffffffu, (r[0] & r[1] & r[2] & r[3]) >= 0 ||
+                                                  r[0] >= 0 || r[1] >= 0 || r[2] >= 0 || r[3] >= 0);
+        if (lane == 0) {
+          ok = !sh.abort_flag && ptx::mbar_wait(smem_u32(&sh.kv_empty[stage]), phase ^ 1);
+          if (!ok && !sh.abort_flag) { sh.abort_flag = 1; raise_status(status, DSA_STATUS_WAIT_TIMEOUT); }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        if (half == 0) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) sh.idx[stage][group * 4 + i] = r[i];
+        }
+        if (lane == 0) sh.live[stage] = live ? 1 : 0;
+        __syncwarp();
+        const uint32_t bar = smem_u32(&sh.kv_full[stage]);
+        if (lane == 0) {
+          if (live) ptx::mbar_expect_tx(bar, kAtStageBytes);
+          else ptx::mbar_arrive(bar);
+        }
+        __syncwarp();
         if (live) {
-          const uint32_t dst0 = kv_addr + stage * kAtStageBytes;
-          int r = ptid / 72, jj = ptid - r * 72;
-#pragma unroll 4
-          for (int it = 0; it < 36; ++it) {
-            const int slot = sh.idx[stage][r];
-            const __nv_bfloat16* src = ckv;
-            if (slot >= 0)
-              src = jj < 64 ? ckv + ((size_t)slot * kCkv + jj * 8) : kpe + ((size_t)slot * kKpe + (jj - 64) * 8);
-            ptx::cp_async16(dst0 + (jj >> 3) * kAtBlockBytes + r * 128 + (((jj & 7) ^ (r & 7)) << 4), src,
-                            slot >= 0 ? 16u : 0u);
-            jj += 56; r += 1;
-            if (jj >= 72) { jj -= 72; r += 1; }
+          // block kb of rows 4*group.. lands at stage + kb*8192 + group*512 (four 128-byte rows)
+          const uint32_t dst = kv_addr + stage * kAtStageBytes + group * 512;
+          if (half == 0) {
+#pragma unroll
+            for (int kb = 0; kb < 5; ++kb)
+              ptx::tma_gather4(dst + kb * kAtBlockBytes, &tmap_ckv, kb * 64, r[0], r[1], r[2], r[3], bar);
+          } else {
+#pragma unroll
+            for (int kb = 5; kb < 8; ++kb)
+              ptx::tma_gather4(dst + kb * kAtBlockBytes, &tmap_ckv, kb * 64, r[0], r[1], r[2], r[3], bar);
+            ptx::tma_gather4(dst + 8 * kAtBlockBytes, &tmap_kpe, 0, r[0], r[1], r[2], r[3], bar);
           }
-        }
-        ptx::cp_async_arrive_noinc(smem_u32(&sh.kv_full[stage]));
-        if (leader) {
-          sh.live[stage] = live ? 1 : 0;
-          ptx::mbar_arrive(smem_u32(&sh.kv_full[stage]));
         }
         stage ^= 1;
         if (stage == 0) phase ^= 1;
@@ -557,22 +589,8 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
   }
 }
 
-static int at_sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
-      cudaGetLastError();
-      n = 0;
-      return 148;
-    }
-  }
-  return n;
-}
-
 size_t at_tc_workspace_bytes_auto(int tokens, int topk) {
-  return at_tc_workspace_bytes(tokens, topk, at_sm_count());
+  return at_tc_workspace_bytes(tokens, topk, sm_count());
 }
 
 cudaError_t launch_sparse_attn_tc(const void* q_nope, const void* q_pe, const void* ckv,
@@ -586,10 +604,15 @@ cudaError_t launch_sparse_attn_tc(const void* q_nope, const void* q_pe, const vo
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  const AtPlan plan = at_make_plan(tokens, topk, at_sm_count());
+  const AtPlan plan = at_make_plan(tokens, topk, sm_count());
+  // flat caches as [num_slots][512] and [num_slots][64] bf16, box = 64 columns x 1 row (gather4)
+  CUtensorMap tmap_ckv, tmap_kpe;
+  if (!make_tmap_2d_sw128(&tmap_ckv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ckv, kCkv, (uint64_t)num_slots, 64, 1) ||
+      !make_tmap_2d_sw128(&tmap_kpe, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, kpe, kKpe, (uint64_t)num_slots, 64, 1))
+    return cudaErrorInvalidValue;
   sparse_attn_tc_kernel<<<plan.grid, kAtThreads, kAtDynBytes, stream>>>(
-      static_cast<const __nv_bfloat16*>(q_nope), static_cast<const __nv_bfloat16*>(q_pe),
-      static_cast<const __nv_bfloat16*>(ckv), static_cast<const __nv_bfloat16*>(kpe), indices,
+      tmap_ckv, tmap_kpe, static_cast<const __nv_bfloat16*>(q_nope),
+      static_cast<const __nv_bfloat16*>(q_pe), indices,
       index_stride, sm_scale * kAtLog2e, static_cast<__nv_bfloat16*>(out), lse, tokens, topk,
       num_slots, plan, ws, status);
   return cudaGetLastError();

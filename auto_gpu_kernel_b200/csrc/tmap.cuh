@@ -1,0 +1,59 @@
+// Host-side TMA tensor-map encoding.  cuTensorMapEncodeTiled is fetched through the runtime's
+// driver entry point query, so the library does not link against libcuda directly.  Maps are
+// encoded per call (about a microsecond) and passed to kernels as __grid_constant__ parameters;
+// nothing is cached on input pointers.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace dsa {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D row-major tensor [rows][inner] of `elem_bytes`-wide elements, box = [box_rows][box_inner],
+// 128-byte swizzle (box_inner * elem_bytes must be <= 128), out-of-range elements read as zero.
+inline bool make_tmap_2d_sw128(CUtensorMap* map, CUtensorMapDataType type, int elem_bytes,
+                               const void* base, uint64_t inner, uint64_t rows, uint32_t box_inner,
+                               uint32_t box_rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (enc == nullptr) return false;
+  cuuint64_t dims[2] = {inner, rows};
+  cuuint64_t strides[1] = {inner * (uint64_t)elem_bytes};
+  cuuint32_t box[2] = {box_inner, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(map, type, 2, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+inline int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = 0;
+      return 148;  // no device visible (host-only tooling): plan for a B200
+    }
+  }
+  return n;
+}
+
+}  // namespace dsa
