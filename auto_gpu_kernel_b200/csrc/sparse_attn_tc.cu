@@ -23,14 +23,15 @@
 // CTA's range covers parts ("segments") of at most a few tokens; a token covered by several CTAs is
 // merged by whichever of them finishes last (atomic arrival counter, nobody waits).
 //
-// Warp roles (192 threads): warps 0-3 softmax + epilogue (TMEM lane quarter = warp), warp 4 MMA
-// issuer, warp 5 gather producer.  The gather uses the TMA tile::gather4 mode: one instruction
-// fetches a 128-byte column block of four arbitrary rows of the flat cache into four consecutive
-// swizzled shared-memory rows (144 instructions per 64-row tile, spread over the 32 lanes); rows
-// with index -1 are out of the tensor and arrive as zeros.  Two stages.
-// Consecutive tcgen05.mma into one accumulator serialise on its latency at N = 16, so S^T is
-// accumulated in four partial accumulators used round-robin (summed after tcgen05.ld) and the PV
-// products are issued k-step-major across the four 128-row output chunks.
+// Warp roles (288 threads): warps 0-3 softmax + epilogue (TMEM lane quarter = warp), warp 4 MMA
+// issuer, warps 5-8 gather producers.  A producer warp instruction copies one 128-byte column
+// block of four rows (8 lanes x 16 B per row, cp.async with zero-fill for masked rows) straight to
+// its swizzled place; a thread keeps its four row indices in registers, so the 36 copies of a
+// tile are address arithmetic with immediates only.  (The TMA tile::gather4 mode was measured
+// here at ~70 cycles per 512-byte instruction, a quarter of what this path sustains.)  Two stages.
+// A tcgen05.mma costs max(45.6, N/2) cycles whatever M is, so at N = 16 the tensor pipe time is
+// instruction count x 46 cycles: descriptors are stepped with one 32-bit add per instruction to
+// keep the issuing thread under that, and S^T uses four partial accumulators round-robin.
 // The running max is only refreshed (and O rescaled in TMEM) when a logit exceeds it by more than
 // 2^8, so the common tile costs one exp2 per logit and no cross-thread reduction; row sums stay
 // per-thread until the end of the segment.  All waits are time-bounded; group decisions are taken
@@ -47,7 +48,7 @@ constexpr int kAtStageBytes = 9 * kAtBlockBytes;   // 73728
 constexpr int kAtQBlockBytes = kHeads * 128;       // 2048
 constexpr int kAtQBytes = 9 * kAtQBlockBytes;      // 18432
 constexpr int kAtPBytes = kHeads * 128;            // 2048
-constexpr int kAtThreads = 192;
+constexpr int kAtThreads = 288;
 constexpr int kAtTmemCols = 256;
 constexpr int kAtSCol = 64;                        // O^T at 0..63; S^T buffer b at 64+64b (4 partials x 16)
 constexpr float kAtLog2e = 1.4426950408889634f;
@@ -57,10 +58,10 @@ constexpr uint32_t kIdescPV = ptx::idesc(ptx::kFmtBF16, ptx::kFmtBF16, true, fal
 
 struct AtShared {
   int idx[2][kAtTile];
-  int live[2];
+  int live_w[2][4];      // per producer warp: the tile has at least one valid row
   int need[4];
   float red[4][kHeads];
-  int go[1][2];
+  int go[2];
   uint64_t kv_full[2], kv_empty[2], q_full[2], q_empty[2];
   uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_free;
   uint32_t tmem_base;
@@ -123,21 +124,23 @@ size_t at_tc_workspace_bytes(int tokens, int topk, int sms) {
   return at_counter_bytes(tokens) + (size_t)tokens * p.segs_max * kHeads * (2 + kCkv) * 4;
 }
 
-// One thread of a 128-thread group waits on an mbarrier (bounded) and the whole group learns the
-// outcome through shared memory, so that a timeout makes all of them leave the loop together.
-__device__ __forceinline__ bool group_wait(AtShared& sh, int group, int& toggle, bool leader,
-                                           uint32_t bar, uint32_t parity, int bar_id,
-                                           int32_t* status) {
+// The softmax group (128 threads) waits on mbarriers through its first thread, which broadcasts
+// the outcome through shared memory: a timeout then makes all of them leave the loop together.
+// `bar2` (0 = none) is waited first; it only adds an acquire on a barrier that is already complete.
+__device__ __forceinline__ bool group_wait(AtShared& sh, int& toggle, bool leader, uint32_t bar2,
+                                           uint32_t bar, uint32_t parity, int32_t* status) {
   if (leader) {
-    bool ok = !sh.abort_flag && ptx::mbar_wait(bar, parity);
+    bool ok = !sh.abort_flag;
+    if (ok && bar2) ok = ptx::mbar_wait(bar2, parity);
+    if (ok) ok = ptx::mbar_wait(bar, parity);
     if (!ok && !sh.abort_flag) {
       sh.abort_flag = 1;
       raise_status(status, DSA_STATUS_WAIT_TIMEOUT);
     }
-    sh.go[group][toggle] = ok ? 1 : 0;
+    sh.go[toggle] = ok ? 1 : 0;
   }
-  ptx::named_bar_sync(bar_id, 128);
-  const bool go = sh.go[group][toggle] != 0;
+  ptx::named_bar_sync(1, 128);
+  const bool go = sh.go[toggle] != 0;
   toggle ^= 1;
   return go;
 }
@@ -179,9 +182,8 @@ __device__ void at_merge_segments(const AtPartials& w, int t, int n_seg, int seg
 }
 
 __global__ void __launch_bounds__(kAtThreads, 1)
-sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_ckv,
-                      const __grid_constant__ CUtensorMap tmap_kpe,
-                      const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloat16* __restrict__ q_pe,
+sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloat16* __restrict__ q_pe,
+                      const __nv_bfloat16* __restrict__ ckv, const __nv_bfloat16* __restrict__ kpe,
                       const int32_t* __restrict__ indices, int64_t index_stride, float scale_log2,
                       __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int tokens, int topk,
                       int64_t num_slots, AtPlan plan, void* ws_raw, int32_t* status) {
@@ -203,9 +205,9 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_ckv,
   if (warp == 4) {
     if (lane == 0) {
       for (int i = 0; i < 2; ++i) {
-        ptx::mbar_init(smem_u32(&sh.kv_full[i]), 1);
-        ptx::mbar_init(smem_u32(&sh.kv_empty[i]), 2);
-        ptx::mbar_init(smem_u32(&sh.q_full[i]), 32);
+        ptx::mbar_init(smem_u32(&sh.kv_full[i]), 128 + 4);  // cp.async arrivals + 4 warp leaders
+        ptx::mbar_init(smem_u32(&sh.kv_empty[i]), 4 + 1);   // softmax warps + MMA
+        ptx::mbar_init(smem_u32(&sh.q_full[i]), 128);
         ptx::mbar_init(smem_u32(&sh.q_empty[i]), 1);
         ptx::mbar_init(smem_u32(&sh.s_full[i]), 1);
         ptx::mbar_init(smem_u32(&sh.s_empty[i]), 4);
@@ -215,8 +217,6 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_ckv,
       ptx::mbar_init(smem_u32(&sh.o_free), 4);
       sh.abort_flag = 0;
       ptx::fence_barrier_init();
-      ptx::prefetch_tensormap(&tmap_ckv);
-      ptx::prefetch_tensormap(&tmap_kpe);
     }
     __syncwarp();
     ptx::tmem_alloc(smem_u32(&sh.tmem_base), kAtTmemCols);
@@ -230,15 +230,17 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_ckv,
   if (w0 < w1) {
     if (warp < 4) {
       // =========================== softmax + epilogue ===========================
+      // Tile i of this CTA uses KV stage i&1 and S^T buffer i&1 (phase (i>>1)&1 of their barriers);
+      // P^T buffers are numbered by live tiles only.
       const bool leader = tid == 0;
       const bool has_row = lane < 16;
       const int row = warp * 16 + (lane & 15);
       const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-      int toggle = 0, stage = 0, phase = 0, n = 0, seg_live = 0;
+      int toggle = 0, i_tile = 0, pl = 0, seg_live = 0;
       long cur_t = -1;
       float m_run[kHeads], l_part[kHeads];
       AtPartials part = at_carve(ws_raw, tokens, plan.segs_max);
-      for (long w = w0; w < w1; ++w) {
+      for (long w = w0; w < w1; ++w, ++i_tile) {
         const long t = w / tpt;
         const int j = (int)(w - t * tpt);
         if (t != cur_t) {
@@ -247,16 +249,13 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_ckv,
           seg_live = 0;
           cur_t = t;
         }
-        if (!group_wait(sh, 0, toggle, leader, smem_u32(&sh.kv_full[stage]), phase, 1, status)) break;
-        const bool live = sh.live[stage] != 0;
-        const bool valid = has_row && sh.idx[stage][row] >= 0;
-        ptx::named_bar_sync(1, 128);
-        if (leader) ptx::mbar_arrive(smem_u32(&sh.kv_empty[stage]));
-        stage ^= 1;
-        if (stage == 0) phase ^= 1;
+        const int sbuf = i_tile & 1, sphase = (i_tile >> 1) & 1;
+        if (!group_wait(sh, toggle, leader, smem_u32(&sh.kv_full[sbuf]), smem_u32(&sh.s_full[sbuf]),
+                        sphase, status)) break;
+        const bool live = (sh.live_w[sbuf][0] | sh.live_w[sbuf][1] | sh.live_w[sbuf][2] | sh.live_w[sbuf][3]) != 0;
+        const bool valid = has_row && sh.idx[sbuf][row] >= 0;
+        float x[kHeads];
         if (live) {
-          const int sbuf = n & 1, sphase = (n >> 1) & 1;
-          if (!group_wait(sh, 0, toggle, leader, smem_u32(&sh.s_full[sbuf]), sphase, 1, status)) break;
           ptx::tc_fence_after();
           uint32_t sr[16], sp1[16], sp2[16], sp3[16];
           const uint32_t s_addr = tmem_base + lane_base + kAtSCol + sbuf * 64;
@@ -267,18 +266,21 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_ckv,
           ptx::tmem_wait_ld();
           ptx::tc_fence_before();
 #pragma unroll
-          for (int h = 0; h < kHeads; ++h)
-            sr[h] = __float_as_uint((__uint_as_float(sr[h]) + __uint_as_float(sp1[h])) +
-                                    (__uint_as_float(sp2[h]) + __uint_as_float(sp3[h])));
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(smem_u32(&sh.s_empty[sbuf]));
-          float x[kHeads];
+          for (int h = 0; h < kHeads; ++h) {
+            const float s4 = (__uint_as_float(sr[h]) + __uint_as_float(sp1[h])) +
+                             (__uint_as_float(sp2[h]) + __uint_as_float(sp3[h]));
+            x[h] = valid ? s4 * scale_log2 : -INFINITY;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) {  // S^T buffer and the stage's index row have been read by this warp
+          ptx::mbar_arrive(smem_u32(&sh.s_empty[sbuf]));
+          ptx::mbar_arrive(smem_u32(&sh.kv_empty[sbuf]));
+        }
+        if (live) {
           bool need = false;
 #pragma unroll
-          for (int h = 0; h < kHeads; ++h) {
-            x[h] = valid ? __uint_as_float(sr[h]) * scale_log2 : -INFINITY;
-            need |= x[h] > m_run[h] + kAtRescaleGap;
-          }
+          for (int h = 0; h < kHeads; ++h) need |= x[h] > m_run[h] + kAtRescaleGap;
           const bool warp_need = __any_sync(0xffffffffu, need);
           if (lane == 0) sh.need[warp] = warp_need;
           ptx::named_bar_sync(1, 128);
@@ -302,10 +304,10 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_ckv,
               l_part[h] *= corr[h];
             }
             if (seg_live > 0) {
-              // PV #(n-1) is complete when P buffer (n-1)&1 has been released for the ((n-1)>>1)-th
-              // time; every phase of that barrier is observed in order, which a parity wait needs.
-              if (!group_wait(sh, 0, toggle, leader, smem_u32(&sh.p_empty[(n - 1) & 1]),
-                              ((n - 1) >> 1) & 1, 1, status)) break;
+              // PV of the previous live tile is complete when its P^T buffer has been released;
+              // every earlier phase of that barrier is known complete (see the P^T write below).
+              if (!group_wait(sh, toggle, leader, 0, smem_u32(&sh.p_empty[(pl - 1) & 1]),
+                              ((pl - 1) >> 1) & 1, status)) break;
               ptx::tc_fence_after();
 #pragma unroll
               for (int c = 0; c < 4; ++c) {
@@ -320,9 +322,11 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_ckv,
               ptx::tc_fence_before();
             }
           }
-          if (!group_wait(sh, 0, toggle, leader, smem_u32(&sh.p_empty[sbuf]), sphase ^ 1, 1, status)) break;
+          // P^T buffer pl&1 was last read by the PV of live tile pl-2.  The MMA thread issued that PV
+          // before this tile's QK, and tcgen05.commit covers everything issued before it, so the
+          // s_full arrival observed above implies that PV is complete: the buffer is free.
           if (has_row) {
-            unsigned char* pb = p_ptr + sbuf * kAtPBytes;
+            unsigned char* pb = p_ptr + (pl & 1) * kAtPBytes;
 #pragma unroll
             for (int h = 0; h < kHeads; ++h) {
               const float m_use = m_run[h] == -INFINITY ? 0.f : m_run[h];
@@ -335,15 +339,15 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_ckv,
           ptx::fence_proxy_async_smem();
           ptx::tc_fence_before();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(smem_u32(&sh.p_full[sbuf]));
-          ++n;
+          if (lane == 0) ptx::mbar_arrive(smem_u32(&sh.p_full[pl & 1]));
+          ++pl;
           ++seg_live;
         }
         if (j == tpt - 1 || w == w1 - 1) {
           // ------------------ end of this CTA's segment of token t ------------------
           if (seg_live > 0) {
-            if (!group_wait(sh, 0, toggle, leader, smem_u32(&sh.p_empty[(n - 1) & 1]),
-                            ((n - 1) >> 1) & 1, 1, status)) break;
+            if (!group_wait(sh, toggle, leader, 0, smem_u32(&sh.p_empty[(pl - 1) & 1]),
+                            ((pl - 1) >> 1) & 1, status)) break;
             ptx::tc_fence_after();
           }
 #pragma unroll
@@ -418,10 +422,15 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_ckv,
     } else if (warp == 4) {
       // =========================== MMA issuer ===========================
       if (lane == 0) {
-        int stage = 0, phase = 0, nq = 0, np = 0, seg_no = 0, qb = 0, qphase = 0, qcur = 0;
+        int i_tile = 0, np = 0, seg_no = 0, qb = 0, qphase = 0;
         long cur_t = -1;
         bool pend = false, pend_first = false, seg_first = true, ok = true;
+        uint32_t pend_a_lo = 0, q_lo = 0;
         int pend_stage = 0;
+        // constant descriptor halves: K-major (LBO 16, SBO 1024) and MN-major (LBO 8192, SBO 1024)
+        const uint64_t dk = ptx::smem_desc_sw128(0, 16, 1024), dmn = ptx::smem_desc_sw128(0, kAtBlockBytes, 1024);
+        const uint32_t k_hi = (uint32_t)(dk >> 32), k_lo0 = (uint32_t)dk;
+        const uint32_t mn_hi = (uint32_t)(dmn >> 32), mn_lo0 = (uint32_t)dmn;
 #define AT_WAIT(bar, parity)                                          \
   if (ok && !(!sh.abort_flag && ptx::mbar_wait(smem_u32(&(bar)), (parity)))) { \
     if (!sh.abort_flag) { sh.abort_flag = 1; raise_status(status, DSA_STATUS_WAIT_TIMEOUT); } \
@@ -432,15 +441,14 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_ckv,
           AT_WAIT(sh.p_full[pbuf], pphase);
           if (!ok) return;
           ptx::tc_fence_after();
-          const uint32_t a0 = kv_addr + pend_stage * kAtStageBytes;
-          const uint32_t b0 = p_addr + pbuf * kAtPBytes;
+          const uint32_t b_lo = k_lo0 + ((p_addr + pbuf * kAtPBytes) >> 4);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-              const uint64_t ad = ptx::smem_desc_sw128(a0 + 2 * c * kAtBlockBytes + ks * 2048, kAtBlockBytes, 1024);
-              const uint64_t bd = ptx::smem_desc_sw128(b0 + ks * 32, 16, 1024);
-              ptx::mma_bf16(tmem_base + c * 16, ad, bd, kIdescPV, !(pend_first && ks == 0));
+              ptx::mma_bf16_split(tmem_base + c * 16, pend_a_lo + ((2 * c * kAtBlockBytes + ks * 2048) >> 4),
+                                  mn_hi, b_lo + ((ks * 32) >> 4), k_hi, kIdescPV,
+                                  (pend_first && ks == 0) ? 0u : 1u);
             }
           }
           ptx::tc_commit(smem_u32(&sh.kv_empty[pend_stage]));
@@ -448,67 +456,68 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_ckv,
           ++np;
           pend = false;
         };
-        for (long w = w0; w < w1 && ok; ++w) {
+        for (long w = w0; w < w1 && ok; ++w, ++i_tile) {
           const long t = w / tpt;
+          const int stage = i_tile & 1, phase = (i_tile >> 1) & 1;
           if (t != cur_t) {
             if (cur_t >= 0) {
               if (pend) issue_pv();
-              ptx::tc_commit(smem_u32(&sh.q_empty[qcur]));
+              ptx::tc_commit(smem_u32(&sh.q_empty[qb ^ 1]));
               AT_WAIT(sh.o_free, seg_no & 1);  // epilogue of the previous segment has read O^T
               ++seg_no;
             }
             AT_WAIT(sh.q_full[qb], qphase);
-            qcur = qb;
+            q_lo = k_lo0 + ((q_addr + qb * kAtQBytes) >> 4);
             qb ^= 1;
             if (qb == 0) qphase ^= 1;
             cur_t = t;
             seg_first = true;
           }
           AT_WAIT(sh.kv_full[stage], phase);
+          AT_WAIT(sh.s_empty[stage], phase ^ 1);
           if (!ok) break;
           ptx::fence_proxy_async_smem();  // cp.async-written tile / q -> visible to the MMA's reads
-          if (sh.live[stage]) {
-            const int sbuf = nq & 1, sphase = (nq >> 1) & 1;
-            AT_WAIT(sh.s_empty[sbuf], sphase ^ 1);
-            if (!ok) break;
+          const bool live = (sh.live_w[stage][0] | sh.live_w[stage][1] | sh.live_w[stage][2] | sh.live_w[stage][3]) != 0;
+          if (live) {
             ptx::tc_fence_after();
-            const uint32_t a0 = kv_addr + stage * kAtStageBytes;
-            const uint32_t b0 = q_addr + qcur * kAtQBytes;
+            const uint32_t a_lo = k_lo0 + ((kv_addr + stage * kAtStageBytes) >> 4);
+            const uint32_t d0 = tmem_base + kAtSCol + stage * 64;
 #pragma unroll
             for (int kb = 0; kb < 9; ++kb) {
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
-                const uint64_t ad = ptx::smem_desc_sw128(a0 + kb * kAtBlockBytes + k * 32, 16, 1024);
-                const uint64_t bd = ptx::smem_desc_sw128(b0 + kb * kAtQBlockBytes + k * 32, 16, 1024);
-                ptx::mma_bf16(tmem_base + kAtSCol + sbuf * 64 + 16 * k, ad, bd, kIdescQK, kb != 0);
+                ptx::mma_bf16_split(d0 + 16 * k, a_lo + ((kb * kAtBlockBytes + k * 32) >> 4), k_hi,
+                                    q_lo + ((kb * kAtQBlockBytes + k * 32) >> 4), k_hi, kIdescQK,
+                                    kb != 0 ? 1u : 0u);
               }
             }
-            ptx::tc_commit(smem_u32(&sh.s_full[sbuf]));
-            ++nq;
+            ptx::tc_commit(smem_u32(&sh.s_full[stage]));
             if (pend) issue_pv();
             pend = true;
+            pend_a_lo = mn_lo0 + ((kv_addr + stage * kAtStageBytes) >> 4);
             pend_stage = stage;
             pend_first = seg_first;
             seg_first = false;
           } else {
+            ptx::mbar_arrive(smem_u32(&sh.s_full[stage]));
             ptx::mbar_arrive(smem_u32(&sh.kv_empty[stage]));
           }
-          stage ^= 1;
-          if (stage == 0) phase ^= 1;
         }
         if (pend && ok) issue_pv();
 #undef AT_WAIT
       }
       __syncwarp();
     } else {
-      // =========================== gather producer (one warp) ===========================
-      int stage = 0, phase = 0, qb = 0, qphase = 0;
+      // =========================== gather producers (4 warps) ===========================
+      const int pw = warp - 5;                       // producer warp 0..3
+      const int sub = lane >> 3, ch = lane & 7;      // row inside a 4-row group, 16-byte chunk of a block
+      int i_tile = 0, qb = 0, qphase = 0;
       long cur_t = -1;
       bool ok = true;
-      const int group = lane & 15, half = lane >> 4;  // lane -> rows 4*group..4*group+3, half of the blocks
-      for (long w = w0; w < w1 && ok; ++w) {
+      for (long w = w0; w < w1; ++w, ++i_tile) {
         const long t = w / tpt;
         const int j = (int)(w - t * tpt);
+        const int stage = i_tile & 1, phase = (i_tile >> 1) & 1;
         if (t != cur_t) {
           if (lane == 0) {
             ok = !sh.abort_flag && ptx::mbar_wait(smem_u32(&sh.q_empty[qb]), qphase ^ 1);
@@ -517,9 +526,10 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_ckv,
           ok = __shfl_sync(0xffffffffu, ok, 0);
           if (!ok) break;
           const uint32_t qdst = q_addr + qb * kAtQBytes;
-#pragma unroll 4
-          for (int it = 0; it < 36; ++it) {
-            const int c = it * 32 + lane, h = c / 72, jj = c - h * 72;
+          const int ptid = pw * 32 + lane;
+#pragma unroll
+          for (int it = 0; it < 9; ++it) {
+            const int c = it * 128 + ptid, h = c / 72, jj = c - h * 72;
             const __nv_bfloat16* src = jj < 64 ? q_nope + ((size_t)(t * kHeads + h) * kCkv + jj * 8)
                                                : q_pe + ((size_t)(t * kHeads + h) * kKpe + (jj - 64) * 8);
             ptx::cp_async16(qdst + (jj >> 3) * kAtQBlockBytes + h * 128 + (((jj & 7) ^ (h & 7)) << 4), src, 16);
@@ -529,51 +539,59 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap tmap_ckv,
           qb ^= 1;
           if (qb == 0) qphase ^= 1;
         }
-        // this lane's four row indices (both halves of the warp read the same 16 groups)
-        int r[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int k = j * kAtTile + group * 4 + i;
-          int v = k < topk ? __ldg(indices + (size_t)t * index_stride + k) : -1;
-          if (v >= num_slots) { raise_status(status, DSA_STATUS_BAD_SLOT); v = -1; }
-          r[i] = v < 0 ? -1 : v;
+        // the tile's 64 indices, two per lane (positions lane and lane+32); every warp reads all of
+        // them so that each knows on its own whether the tile has any valid row
+        int v0, v1;
+        {
+          const int k0 = j * kAtTile + lane, k1 = k0 + 32;
+          v0 = k0 < topk ? __ldg(indices + (size_t)t * index_stride + k0) : -1;
+          v1 = k1 < topk ? __ldg(indices + (size_t)t * index_stride + k1) : -1;
+          if (v0 >= num_slots || v1 >= num_slots) {
+            raise_status(status, DSA_STATUS_BAD_SLOT);
+            if (v0 >= num_slots) v0 = -1;
+            if (v1 >= num_slots) v1 = -1;
+          }
+          if (v0 < 0) v0 = -1;
+          if (v1 < 0) v1 = -1;
         }
-        const bool live = __any_sync(0xffffffffu, (r[0] & r[1] & r[2] & r[3]) >= 0 ||
-                                                  r[0] >= 0 || r[1] >= 0 || r[2] >= 0 || r[3] >= 0);
+        const bool live = __any_sync(0xffffffffu, v0 >= 0 || v1 >= 0);
+        // rows of this thread: group g = pw + 4*gi, row = 4*g + sub
+        int slot[4];
+#pragma unroll
+        for (int gi = 0; gi < 4; ++gi) {
+          const int r = 4 * (pw + 4 * gi) + sub;
+          const int a = __shfl_sync(0xffffffffu, v0, r & 31), b = __shfl_sync(0xffffffffu, v1, r & 31);
+          slot[gi] = r < 32 ? a : b;
+        }
         if (lane == 0) {
           ok = !sh.abort_flag && ptx::mbar_wait(smem_u32(&sh.kv_empty[stage]), phase ^ 1);
           if (!ok && !sh.abort_flag) { sh.abort_flag = 1; raise_status(status, DSA_STATUS_WAIT_TIMEOUT); }
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) break;
-        if (half == 0) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) sh.idx[stage][group * 4 + i] = r[i];
-        }
-        if (lane == 0) sh.live[stage] = live ? 1 : 0;
-        __syncwarp();
-        const uint32_t bar = smem_u32(&sh.kv_full[stage]);
-        if (lane == 0) {
-          if (live) ptx::mbar_expect_tx(bar, kAtStageBytes);
-          else ptx::mbar_arrive(bar);
-        }
-        __syncwarp();
         if (live) {
-          // block kb of rows 4*group.. lands at stage + kb*8192 + group*512 (four 128-byte rows)
-          const uint32_t dst = kv_addr + stage * kAtStageBytes + group * 512;
-          if (half == 0) {
+          const uint32_t dst0 = kv_addr + stage * kAtStageBytes;
 #pragma unroll
-            for (int kb = 0; kb < 5; ++kb)
-              ptx::tma_gather4(dst + kb * kAtBlockBytes, &tmap_ckv, kb * 64, r[0], r[1], r[2], r[3], bar);
-          } else {
+          for (int gi = 0; gi < 4; ++gi) {
+            const int r = 4 * (pw + 4 * gi) + sub;
+            const int sl = slot[gi];
+            const uint32_t nbytes = sl >= 0 ? 16u : 0u;
+            const __nv_bfloat16* src_c = ckv + ((size_t)(sl >= 0 ? sl : 0) * kCkv + ch * 8);
+            const __nv_bfloat16* src_p = kpe + ((size_t)(sl >= 0 ? sl : 0) * kKpe + ch * 8);
+            const uint32_t dst = dst0 + r * 128 + ((ch ^ (r & 7)) << 4);
 #pragma unroll
-            for (int kb = 5; kb < 8; ++kb)
-              ptx::tma_gather4(dst + kb * kAtBlockBytes, &tmap_ckv, kb * 64, r[0], r[1], r[2], r[3], bar);
-            ptx::tma_gather4(dst + 8 * kAtBlockBytes, &tmap_kpe, 0, r[0], r[1], r[2], r[3], bar);
+            for (int kb = 0; kb < 8; ++kb) ptx::cp_async16(dst + kb * kAtBlockBytes, src_c + kb * 64, nbytes);
+            ptx::cp_async16(dst + 8 * kAtBlockBytes, src_p, nbytes);
           }
         }
-        stage ^= 1;
-        if (stage == 0) phase ^= 1;
+        if (ch == 0) {
+#pragma unroll
+          for (int gi = 0; gi < 4; ++gi) sh.idx[stage][4 * (pw + 4 * gi) + sub] = slot[gi];
+        }
+        if (lane == 0) sh.live_w[stage][pw] = live ? 1 : 0;
+        ptx::cp_async_arrive_noinc(smem_u32(&sh.kv_full[stage]));
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(smem_u32(&sh.kv_full[stage]));
       }
       ptx::cp_async_wait_all();
     }
@@ -605,14 +623,9 @@ cudaError_t launch_sparse_attn_tc(const void* q_nope, const void* q_pe, const vo
     attr_set = true;
   }
   const AtPlan plan = at_make_plan(tokens, topk, sm_count());
-  // flat caches as [num_slots][512] and [num_slots][64] bf16, box = 64 columns x 1 row (gather4)
-  CUtensorMap tmap_ckv, tmap_kpe;
-  if (!make_tmap_2d_sw128(&tmap_ckv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ckv, kCkv, (uint64_t)num_slots, 64, 1) ||
-      !make_tmap_2d_sw128(&tmap_kpe, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, kpe, kKpe, (uint64_t)num_slots, 64, 1))
-    return cudaErrorInvalidValue;
   sparse_attn_tc_kernel<<<plan.grid, kAtThreads, kAtDynBytes, stream>>>(
-      tmap_ckv, tmap_kpe, static_cast<const __nv_bfloat16*>(q_nope),
-      static_cast<const __nv_bfloat16*>(q_pe), indices,
+      static_cast<const __nv_bfloat16*>(q_nope), static_cast<const __nv_bfloat16*>(q_pe),
+      static_cast<const __nv_bfloat16*>(ckv), static_cast<const __nv_bfloat16*>(kpe), indices,
       index_stride, sm_scale * kAtLog2e, static_cast<__nv_bfloat16*>(out), lse, tokens, topk,
       num_slots, plan, ws, status);
   return cudaGetLastError();
