@@ -421,90 +421,119 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
       }
     } else if (warp == 4) {
       // =========================== MMA issuer ===========================
+      // Event loop of one thread: a PV product is issued as soon as the softmax warps have
+      // published its P^T (that frees the tile's stage for the next gather at the earliest
+      // moment); otherwise the QK product of the next tile is issued once its gather has landed.
+      // Up to two PV products can be pending (tile i+1 scored before tile i is weighted).
       if (lane == 0) {
-        int i_tile = 0, np = 0, seg_no = 0, qb = 0, qphase = 0;
+        const int n_tiles = (int)(w1 - w0);
+        int qk_i = 0, np = 0, seg_no = 0, qb = 0, qphase = 0;
         long cur_t = -1;
-        bool pend = false, pend_first = false, seg_first = true, ok = true;
-        uint32_t pend_a_lo = 0, q_lo = 0;
-        int pend_stage = 0;
+        bool seg_first = true, ok = true;
+        uint32_t q_lo = 0;
+        int pend_n = 0, pend_stage[2] = {0, 0};
+        bool pend_first[2] = {false, false};
         // constant descriptor halves: K-major (LBO 16, SBO 1024) and MN-major (LBO 8192, SBO 1024)
         const uint64_t dk = ptx::smem_desc_sw128(0, 16, 1024), dmn = ptx::smem_desc_sw128(0, kAtBlockBytes, 1024);
         const uint32_t k_hi = (uint32_t)(dk >> 32), k_lo0 = (uint32_t)dk;
         const uint32_t mn_hi = (uint32_t)(dmn >> 32), mn_lo0 = (uint32_t)dmn;
-#define AT_WAIT(bar, parity)                                          \
-  if (ok && !(!sh.abort_flag && ptx::mbar_wait(smem_u32(&(bar)), (parity)))) { \
-    if (!sh.abort_flag) { sh.abort_flag = 1; raise_status(status, DSA_STATUS_WAIT_TIMEOUT); } \
-    ok = false;                                                       \
-  }
-        auto issue_pv = [&]() {
-          const int pbuf = np & 1, pphase = (np >> 1) & 1;
-          AT_WAIT(sh.p_full[pbuf], pphase);
-          if (!ok) return;
+        auto fail = [&]() {
+          if (!sh.abort_flag) { sh.abort_flag = 1; raise_status(status, DSA_STATUS_WAIT_TIMEOUT); }
+          ok = false;
+        };
+        auto wait = [&](uint64_t& bar, uint32_t parity) {
+          if (ok && !(!sh.abort_flag && ptx::mbar_wait(smem_u32(&bar), parity))) fail();
+        };
+        auto issue_pv = [&]() {  // head of the pending queue; its P^T is known to be published
+          const int pbuf = np & 1, st = pend_stage[0];
           ptx::tc_fence_after();
+          const uint32_t a_lo = mn_lo0 + ((kv_addr + st * kAtStageBytes) >> 4);
           const uint32_t b_lo = k_lo0 + ((p_addr + pbuf * kAtPBytes) >> 4);
+          const bool first = pend_first[0];
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-              ptx::mma_bf16_split(tmem_base + c * 16, pend_a_lo + ((2 * c * kAtBlockBytes + ks * 2048) >> 4),
+              ptx::mma_bf16_split(tmem_base + c * 16, a_lo + ((2 * c * kAtBlockBytes + ks * 2048) >> 4),
                                   mn_hi, b_lo + ((ks * 32) >> 4), k_hi, kIdescPV,
-                                  (pend_first && ks == 0) ? 0u : 1u);
+                                  (first && ks == 0) ? 0u : 1u);
             }
           }
-          ptx::tc_commit(smem_u32(&sh.kv_empty[pend_stage]));
+          ptx::tc_commit(smem_u32(&sh.kv_empty[st]));
           ptx::tc_commit(smem_u32(&sh.p_empty[pbuf]));
           ++np;
-          pend = false;
+          pend_stage[0] = pend_stage[1];
+          pend_first[0] = pend_first[1];
+          --pend_n;
         };
-        for (long w = w0; w < w1 && ok; ++w, ++i_tile) {
-          const long t = w / tpt;
-          const int stage = i_tile & 1, phase = (i_tile >> 1) & 1;
-          if (t != cur_t) {
-            if (cur_t >= 0) {
-              if (pend) issue_pv();
-              ptx::tc_commit(smem_u32(&sh.q_empty[qb ^ 1]));
-              AT_WAIT(sh.o_free, seg_no & 1);  // epilogue of the previous segment has read O^T
-              ++seg_no;
-            }
-            AT_WAIT(sh.q_full[qb], qphase);
-            q_lo = k_lo0 + ((q_addr + qb * kAtQBytes) >> 4);
-            qb ^= 1;
-            if (qb == 0) qphase ^= 1;
-            cur_t = t;
-            seg_first = true;
-          }
-          AT_WAIT(sh.kv_full[stage], phase);
-          AT_WAIT(sh.s_empty[stage], phase ^ 1);
-          if (!ok) break;
-          ptx::fence_proxy_async_smem();  // cp.async-written tile / q -> visible to the MMA's reads
-          const bool live = (sh.live_w[stage][0] | sh.live_w[stage][1] | sh.live_w[stage][2] | sh.live_w[stage][3]) != 0;
-          if (live) {
-            ptx::tc_fence_after();
-            const uint32_t a_lo = k_lo0 + ((kv_addr + stage * kAtStageBytes) >> 4);
-            const uint32_t d0 = tmem_base + kAtSCol + stage * 64;
-#pragma unroll
-            for (int kb = 0; kb < 9; ++kb) {
-#pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                ptx::mma_bf16_split(d0 + 16 * k, a_lo + ((kb * kAtBlockBytes + k * 32) >> 4), k_hi,
-                                    q_lo + ((kb * kAtQBlockBytes + k * 32) >> 4), k_hi, kIdescQK,
-                                    kb != 0 ? 1u : 0u);
+        uint64_t idle_since = 0;
+        while (ok && (qk_i < n_tiles || pend_n > 0)) {
+          bool progressed = false;
+          if (pend_n > 0 && ptx::mbar_try_wait(smem_u32(&sh.p_full[np & 1]), (np >> 1) & 1)) {
+            issue_pv();
+            progressed = true;
+          } else if (qk_i < n_tiles) {
+            const long w = w0 + qk_i;
+            const long t = w / tpt;
+            const int stage = qk_i & 1, phase = (qk_i >> 1) & 1;
+            if (t != cur_t) {
+              // segment switch: everything of the previous segment must be issued and read first
+              if (cur_t >= 0) {
+                while (ok && pend_n > 0) {
+                  wait(sh.p_full[np & 1], (np >> 1) & 1);
+                  if (ok) issue_pv();
+                }
+                ptx::tc_commit(smem_u32(&sh.q_empty[qb ^ 1]));
+                wait(sh.o_free, seg_no & 1);  // epilogue of the previous segment has read O^T
+                ++seg_no;
               }
+              wait(sh.q_full[qb], qphase);
+              if (!ok) break;
+              q_lo = k_lo0 + ((q_addr + qb * kAtQBytes) >> 4);
+              qb ^= 1;
+              if (qb == 0) qphase ^= 1;
+              cur_t = t;
+              seg_first = true;
+              progressed = true;
+            } else if (pend_n < 2 && ptx::mbar_try_wait(smem_u32(&sh.kv_full[stage]), phase) &&
+                       ptx::mbar_try_wait(smem_u32(&sh.s_empty[stage]), phase ^ 1)) {
+              ptx::fence_proxy_async_smem();  // cp.async-written tile / q -> visible to the MMA's reads
+              const bool live = (sh.live_w[stage][0] | sh.live_w[stage][1] | sh.live_w[stage][2] |
+                                 sh.live_w[stage][3]) != 0;
+              if (live) {
+                ptx::tc_fence_after();
+                const uint32_t a_lo = k_lo0 + ((kv_addr + stage * kAtStageBytes) >> 4);
+                const uint32_t d0 = tmem_base + kAtSCol + stage * 64;
+#pragma unroll
+                for (int kb = 0; kb < 9; ++kb) {
+#pragma unroll
+                  for (int k = 0; k < 4; ++k) {
+                    ptx::mma_bf16_split(d0 + 16 * k, a_lo + ((kb * kAtBlockBytes + k * 32) >> 4), k_hi,
+                                        q_lo + ((kb * kAtQBlockBytes + k * 32) >> 4), k_hi, kIdescQK,
+                                        kb != 0 ? 1u : 0u);
+                  }
+                }
+                ptx::tc_commit(smem_u32(&sh.s_full[stage]));
+                pend_stage[pend_n] = stage;
+                pend_first[pend_n] = seg_first;
+                ++pend_n;
+                seg_first = false;
+              } else {
+                ptx::mbar_arrive(smem_u32(&sh.s_full[stage]));
+                ptx::mbar_arrive(smem_u32(&sh.kv_empty[stage]));
+              }
+              ++qk_i;
+              progressed = true;
             }
-            ptx::tc_commit(smem_u32(&sh.s_full[stage]));
-            if (pend) issue_pv();
-            pend = true;
-            pend_a_lo = mn_lo0 + ((kv_addr + stage * kAtStageBytes) >> 4);
-            pend_stage = stage;
-            pend_first = seg_first;
-            seg_first = false;
+          }
+          if (progressed) {
+            idle_since = 0;
           } else {
-            ptx::mbar_arrive(smem_u32(&sh.s_full[stage]));
-            ptx::mbar_arrive(smem_u32(&sh.kv_empty[stage]));
+            const uint64_t now = ptx::global_timer_ns();
+            if (idle_since == 0) idle_since = now;
+            else if (now - idle_since > 250000000ull || sh.abort_flag) fail();
           }
         }
-        if (pend && ok) issue_pv();
-#undef AT_WAIT
       }
       __syncwarp();
     } else {
