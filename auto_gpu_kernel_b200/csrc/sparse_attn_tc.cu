@@ -543,9 +543,16 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
       int i_tile = 0, qb = 0, qphase = 0;
       long cur_t = -1;
       bool ok = true;
+      auto load_indices = [&](long wt, int& a, int& b) {
+        const long tt = wt / tpt;
+        const int k0 = (int)(wt - tt * tpt) * kAtTile + lane, k1 = k0 + 32;
+        a = k0 < topk ? __ldg(indices + (size_t)tt * index_stride + k0) : -1;
+        b = k1 < topk ? __ldg(indices + (size_t)tt * index_stride + k1) : -1;
+      };
+      int nv0, nv1;
+      load_indices(w0, nv0, nv1);
       for (long w = w0; w < w1; ++w, ++i_tile) {
         const long t = w / tpt;
-        const int j = (int)(w - t * tpt);
         const int stage = i_tile & 1, phase = (i_tile >> 1) & 1;
         if (t != cur_t) {
           if (lane == 0) {
@@ -569,20 +576,17 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
           if (qb == 0) qphase ^= 1;
         }
         // the tile's 64 indices, two per lane (positions lane and lane+32); every warp reads all of
-        // them so that each knows on its own whether the tile has any valid row
-        int v0, v1;
-        {
-          const int k0 = j * kAtTile + lane, k1 = k0 + 32;
-          v0 = k0 < topk ? __ldg(indices + (size_t)t * index_stride + k0) : -1;
-          v1 = k1 < topk ? __ldg(indices + (size_t)t * index_stride + k1) : -1;
-          if (v0 >= num_slots || v1 >= num_slots) {
-            raise_status(status, DSA_STATUS_BAD_SLOT);
-            if (v0 >= num_slots) v0 = -1;
-            if (v1 >= num_slots) v1 = -1;
-          }
-          if (v0 < 0) v0 = -1;
-          if (v1 < 0) v1 = -1;
+        // them so that each knows on its own whether the tile has any valid row.  They were
+        // requested one tile ahead, so their latency is hidden behind the previous tile's copies.
+        int v0 = nv0, v1 = nv1;
+        if (w + 1 < w1) load_indices(w + 1, nv0, nv1);
+        if (v0 >= num_slots || v1 >= num_slots) {
+          raise_status(status, DSA_STATUS_BAD_SLOT);
+          if (v0 >= num_slots) v0 = -1;
+          if (v1 >= num_slots) v1 = -1;
         }
+        if (v0 < 0) v0 = -1;
+        if (v1 < 0) v1 = -1;
         const bool live = __any_sync(0xffffffffu, v0 >= 0 || v1 >= 0);
         // rows of this thread: group g = pw + 4*gi, row = 4*g + sub
         int slot[4];
