@@ -240,9 +240,10 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
       long cur_t = -1;
       float m_run[kHeads], l_part[kHeads];
       AtPartials part = at_carve(ws_raw, tokens, plan.segs_max);
+      long t = w0 / tpt;
+      int j = (int)(w0 - t * tpt) - 1;
       for (long w = w0; w < w1; ++w, ++i_tile) {
-        const long t = w / tpt;
-        const int j = (int)(w - t * tpt);
+        if (++j == tpt) { j = 0; ++t; }
         if (t != cur_t) {
 #pragma unroll
           for (int h = 0; h < kHeads; ++h) { m_run[h] = -INFINITY; l_part[h] = 0.f; }
@@ -428,7 +429,8 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
       if (lane == 0) {
         const int n_tiles = (int)(w1 - w0);
         int qk_i = 0, np = 0, seg_no = 0, qb = 0, qphase = 0;
-        long cur_t = -1;
+        long cur_t = -1, t = w0 / tpt;
+        int j = (int)(w0 - t * tpt);  // (t, j) of tile qk_i
         bool seg_first = true, ok = true;
         uint32_t q_lo = 0;
         int pend_n = 0, pend_stage[2] = {0, 0};
@@ -473,8 +475,6 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
             issue_pv();
             progressed = true;
           } else if (qk_i < n_tiles) {
-            const long w = w0 + qk_i;
-            const long t = w / tpt;
             const int stage = qk_i & 1, phase = (qk_i >> 1) & 1;
             if (t != cur_t) {
               // segment switch: everything of the previous segment must be issued and read first
@@ -512,6 +512,12 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
                                         q_lo + ((kb * kAtQBlockBytes + k * 32) >> 4), k_hi, kIdescQK,
                                         kb != 0 ? 1u : 0u);
                   }
+                  // a PV whose P^T shows up meanwhile goes first: it frees a stage for the gather
+                  if ((kb == 2 || kb == 5) && pend_n > 0 &&
+                      ptx::mbar_try_wait(smem_u32(&sh.p_full[np & 1]), (np >> 1) & 1)) {
+                    issue_pv();
+                    ptx::tc_fence_after();
+                  }
                 }
                 ptx::tc_commit(smem_u32(&sh.s_full[stage]));
                 pend_stage[pend_n] = stage;
@@ -523,6 +529,7 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
                 ptx::mbar_arrive(smem_u32(&sh.kv_empty[stage]));
               }
               ++qk_i;
+              if (++j == tpt) { j = 0; ++t; }
               progressed = true;
             }
           }
@@ -543,16 +550,16 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
       int i_tile = 0, qb = 0, qphase = 0;
       long cur_t = -1;
       bool ok = true;
-      auto load_indices = [&](long wt, int& a, int& b) {
-        const long tt = wt / tpt;
-        const int k0 = (int)(wt - tt * tpt) * kAtTile + lane, k1 = k0 + 32;
+      auto load_indices = [&](long tt, int jj, int& a, int& b) {
+        const int k0 = jj * kAtTile + lane, k1 = k0 + 32;
         a = k0 < topk ? __ldg(indices + (size_t)tt * index_stride + k0) : -1;
         b = k1 < topk ? __ldg(indices + (size_t)tt * index_stride + k1) : -1;
       };
+      long t = w0 / tpt;
+      int j = (int)(w0 - t * tpt);
       int nv0, nv1;
-      load_indices(w0, nv0, nv1);
+      load_indices(t, j, nv0, nv1);
       for (long w = w0; w < w1; ++w, ++i_tile) {
-        const long t = w / tpt;
         const int stage = i_tile & 1, phase = (i_tile >> 1) & 1;
         if (t != cur_t) {
           if (lane == 0) {
@@ -579,7 +586,10 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
         // them so that each knows on its own whether the tile has any valid row.  They were
         // requested one tile ahead, so their latency is hidden behind the previous tile's copies.
         int v0 = nv0, v1 = nv1;
-        if (w + 1 < w1) load_indices(w + 1, nv0, nv1);
+        long t_next = t;
+        int j_next = j + 1;
+        if (j_next == tpt) { j_next = 0; ++t_next; }
+        if (w + 1 < w1) load_indices(t_next, j_next, nv0, nv1);
         if (v0 >= num_slots || v1 >= num_slots) {
           raise_status(status, DSA_STATUS_BAD_SLOT);
           if (v0 >= num_slots) v0 = -1;
@@ -625,6 +635,8 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
         ptx::cp_async_arrive_noinc(smem_u32(&sh.kv_full[stage]));
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(smem_u32(&sh.kv_full[stage]));
+        t = t_next;
+        j = j_next;
       }
       ptx::cp_async_wait_all();
     }

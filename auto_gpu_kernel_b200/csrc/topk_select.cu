@@ -23,12 +23,14 @@ constexpr int kSelThreads = 1024;
 constexpr int kSelRowCap = 49152;  // scores staged in dynamic shared memory (192 KB)
 constexpr int kSelBins = 2048;
 constexpr int kSelCandCap = 1024;
+constexpr int kSelTableCap = 2048;      // block_table entries staged in shared memory (128K tokens)
 constexpr float kSelFloor = -3.0e38f;  // -inf / NaN scores are ranked as this value
 
 struct SelShared {
   uint32_t hist[kSelBins];
   uint32_t cand_key[kSelCandCap];
   int cand_idx[kSelCandCap];
+  int32_t table[kSelTableCap];
   uint32_t warp_sums[32];
   uint32_t red_a[32], red_b[32];
   uint32_t digit, above, ties, cnt_gt, cnt_gt2, cnt_eq, cnt_cand, kmin, kmax;
@@ -94,11 +96,20 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   int32_t* out_row = out + (size_t)b * out_stride;
   const int32_t* table = block_table + (size_t)b * bt_stride;
   const float* row = scores + (size_t)b * score_stride;
-  auto slot_of = [&](int i) -> int32_t { return table[i >> 6] * kPage + (i & 63); };
+  const int n_pages = (len + kPage - 1) / kPage;
+  const bool table_staged = n_pages <= kSelTableCap;
+  // the emit loops would otherwise pay a dependent global load per selected element
+  auto slot_of = [&](int i) -> int32_t {
+    return (table_staged ? sh.table[i >> 6] : table[i >> 6]) * kPage + (i & 63);
+  };
 
   if (len <= kTopK) {  // every token is selected: no scores needed
-    for (int i = tid; i < kTopK; i += kSelThreads) out_row[i] = i < len ? slot_of(i) : -1;
+    for (int i = tid; i < kTopK; i += kSelThreads)
+      out_row[i] = i < len ? table[i >> 6] * kPage + (i & 63) : -1;
     return;
+  }
+  if (table_staged) {
+    for (int i = tid; i < n_pages; i += kSelThreads) sh.table[i] = table[i];
   }
 
   const bool staged = len <= kSelRowCap;
@@ -154,26 +165,33 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   __syncthreads();
 
   // ---- sweep C: emit everything above the boundary bin, collect the boundary bin ---------------
+  // Each thread first counts its own elements above the boundary, a warp scan plus ONE shared
+  // atomic per warp hands out contiguous output slots, then the elements are written: no atomic
+  // (and no dependent round trip) inside the per-element loops.
   const int sweeps = (len + kSelThreads - 1) / kSelThreads;
-  for (int s = 0; s < sweeps; ++s) {
-    const int i = s * kSelThreads + tid;
-    float v = 0.f;
-    int bin = -1;
-    if (i < len) { v = value_at(i); bin = bin_of(v); }
-    const bool gt = bin > edge;
-    const uint32_t m = __ballot_sync(0xffffffffu, gt);
-    if (m) {
-      uint32_t base = 0;
-      if (lane == 0) base = atomicAdd(&sh.cnt_gt, __popc(m));
-      base = __shfl_sync(0xffffffffu, base, 0);
-      if (gt) {
-        const uint32_t pos = base + __popc(m & ((1u << lane) - 1));
-        if (pos < (uint32_t)kTopK) out_row[pos] = slot_of(i);
-      }
+  {
+    uint32_t mine = 0;
+    for (int i = tid; i < len; i += kSelThreads) mine += bin_of(value_at(i)) > edge ? 1u : 0u;
+    uint32_t incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
     }
-    if (few && bin == edge) {
-      const uint32_t c = atomicAdd(&sh.cnt_cand, 1u);
-      if (c < (uint32_t)kSelCandCap) { sh.cand_key[c] = float_to_ordered(v); sh.cand_idx[c] = i; }
+    uint32_t base = 0;
+    if (lane == 31) base = atomicAdd(&sh.cnt_gt, incl);
+    base = __shfl_sync(0xffffffffu, base, 31);
+    uint32_t pos = base + incl - mine;
+    for (int i = tid; i < len; i += kSelThreads) {
+      const float v = value_at(i);
+      const int bin = bin_of(v);
+      if (bin > edge) {
+        if (pos < (uint32_t)kTopK) out_row[pos] = slot_of(i);
+        ++pos;
+      } else if (few && bin == edge) {
+        const uint32_t c = atomicAdd(&sh.cnt_cand, 1u);
+        if (c < (uint32_t)kSelCandCap) { sh.cand_key[c] = float_to_ordered(v); sh.cand_idx[c] = i; }
+      }
     }
   }
   __syncthreads();
