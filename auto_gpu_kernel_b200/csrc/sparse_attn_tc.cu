@@ -61,6 +61,8 @@ struct AtShared {
   int live_w[2][4];      // per producer warp: the tile has at least one valid row
   int need[4];
   float red[4][kHeads];
+  float merge_f[32][kHeads];  // per-segment rescale factors of the token being merged
+  float merge_inv[kHeads];
   int go[2];
   uint64_t kv_full[2], kv_empty[2], q_full[2], q_empty[2];
   uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_free;
@@ -112,8 +114,12 @@ AtPlan at_make_plan(int tokens, int topk, int sms) {
     p.segs_max = 1;
   } else {
     p.per_cta = (int)((total + p.grid - 1) / p.grid);
+    // a token may be cut into at most 32 segments (size of the merge scratch in shared memory)
+    const int min_per = (p.tiles_per_token + 30) / 31;
+    if (p.per_cta < min_per) p.per_cta = min_per;
     int s = (p.tiles_per_token + p.per_cta - 1) / p.per_cta + 1;
     p.segs_max = s < p.tiles_per_token ? s : p.tiles_per_token;
+    if (p.segs_max > 32) p.segs_max = 32;
   }
   p.grid = (int)((total + p.per_cta - 1) / p.per_cta);
   return p;
@@ -145,40 +151,46 @@ __device__ __forceinline__ bool group_wait(AtShared& sh, int& toggle, bool leade
   return go;
 }
 
-__device__ void at_merge_segments(const AtPartials& w, int t, int n_seg, int segs_max,
+// Merge the per-segment partial results of one token (run by the 128 softmax threads of the CTA
+// that arrived last).  Threads 0..15 turn the segments' (m, l) into rescale factors; then every
+// thread owns four consecutive output columns and walks the 16 heads, so each warp reads 512
+// contiguous bytes per (segment, head) and the loads of different heads are independent.
+__device__ void at_merge_segments(AtShared& sh, const AtPartials& w, int t, int n_seg, int segs_max,
                                   __nv_bfloat16* out, float* lse, int tid) {
-  // 128 threads: head = tid / 8, 64 output columns each
-  const int h = tid >> 3, c0 = (tid & 7) * 64;
-  float mx = -INFINITY;
-  for (int s = 0; s < n_seg; ++s) mx = fmaxf(mx, w.m[((size_t)t * segs_max + s) * kHeads + h]);
-  float lsum = 0.f;
-  float f[8];
-  for (int s = 0; s < n_seg; ++s) {
-    size_t o = ((size_t)t * segs_max + s) * kHeads + h;
-    float ms = w.m[o];
-    float fs = (ms == -INFINITY) ? 0.f : exp2f(ms - mx);
-    if (s < 8) f[s] = fs;
-    lsum += w.l[o] * fs;
-  }
-  const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-  __nv_bfloat16* dst = out + ((size_t)t * kHeads + h) * kCkv + c0;
-  for (int j = 0; j < 64; j += 4) {
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (tid < kHeads) {
+    const int h = tid;
+    float mx = -INFINITY;
+    for (int s = 0; s < n_seg; ++s) mx = fmaxf(mx, w.m[((size_t)t * segs_max + s) * kHeads + h]);
+    float lsum = 0.f;
     for (int s = 0; s < n_seg; ++s) {
-      size_t o = ((size_t)t * segs_max + s) * kHeads + h;
-      float fs;
-      if (s < 8) fs = f[s];
-      else { float ms = w.m[o]; fs = (ms == -INFINITY) ? 0.f : exp2f(ms - mx); }
-      if (fs == 0.f) continue;
-      float4 v = *reinterpret_cast<const float4*>(w.acc + o * kCkv + c0 + j);
-      a.x += v.x * fs; a.y += v.y * fs; a.z += v.z * fs; a.w += v.w * fs;
+      const size_t o = ((size_t)t * segs_max + s) * kHeads + h;
+      const float ms = w.m[o];
+      const float fs = (ms == -INFINITY) ? 0.f : exp2f(ms - mx);
+      sh.merge_f[s][h] = fs;
+      lsum += w.l[o] * fs;
     }
-    *reinterpret_cast<__nv_bfloat162*>(dst + j) = __floats2bfloat162_rn(a.x * inv, a.y * inv);
-    *reinterpret_cast<__nv_bfloat162*>(dst + j + 2) = __floats2bfloat162_rn(a.z * inv, a.w * inv);
-  }
-  if ((tid & 7) == 0) {
+    sh.merge_inv[h] = lsum > 0.f ? 1.f / lsum : 0.f;
     lse[(size_t)t * kHeads + h] = lsum > 0.f ? mx + log2f(lsum) : -INFINITY;
   }
+  ptx::named_bar_sync(1, 128);
+  const int c0 = tid * 4;
+#pragma unroll 4
+  for (int h = 0; h < kHeads; ++h) {
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < n_seg; ++s) {
+      const float fs = sh.merge_f[s][h];
+      if (fs == 0.f) continue;
+      const float4 v = *reinterpret_cast<const float4*>(
+          w.acc + (((size_t)t * segs_max + s) * kHeads + h) * kCkv + c0);
+      a.x += v.x * fs; a.y += v.y * fs; a.z += v.z * fs; a.w += v.w * fs;
+    }
+    const float inv = sh.merge_inv[h];
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a.x * inv, a.y * inv);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(a.z * inv, a.w * inv);
+    uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    *reinterpret_cast<uint2*>(out + ((size_t)t * kHeads + h) * kCkv + c0) = packed;
+  }
+  ptx::named_bar_sync(1, 128);  // merge_f / merge_inv may be rewritten by a later merge
 }
 
 __global__ void __launch_bounds__(kAtThreads, 1)
@@ -415,7 +427,7 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
             ptx::named_bar_sync(1, 128);
             if (sh.is_last) {
               __threadfence();
-              at_merge_segments(part, (int)t, n_seg, plan.segs_max, out, lse, tid);
+              at_merge_segments(sh, part, (int)t, n_seg, plan.segs_max, out, lse, tid);
             }
           }
         }
