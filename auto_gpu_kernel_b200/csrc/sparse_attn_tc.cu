@@ -174,19 +174,25 @@ __device__ void at_merge_segments(AtShared& sh, const AtPartials& w, int t, int 
   }
   ptx::named_bar_sync(1, 128);
   const int c0 = tid * 4;
-#pragma unroll 4
-  for (int h = 0; h < kHeads; ++h) {
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < n_seg; ++s) {
+  float4 a[kHeads];
+#pragma unroll
+  for (int h = 0; h < kHeads; ++h) a[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < n_seg; ++s) {
+    const float* base = w.acc + ((size_t)t * segs_max + s) * kHeads * kCkv + c0;
+    float4 v[kHeads];
+#pragma unroll
+    for (int h = 0; h < kHeads; ++h) v[h] = *reinterpret_cast<const float4*>(base + h * kCkv);  // 16 loads in flight
+#pragma unroll
+    for (int h = 0; h < kHeads; ++h) {
       const float fs = sh.merge_f[s][h];
-      if (fs == 0.f) continue;
-      const float4 v = *reinterpret_cast<const float4*>(
-          w.acc + (((size_t)t * segs_max + s) * kHeads + h) * kCkv + c0);
-      a.x += v.x * fs; a.y += v.y * fs; a.z += v.z * fs; a.w += v.w * fs;
+      a[h].x += v[h].x * fs; a[h].y += v[h].y * fs; a[h].z += v[h].z * fs; a[h].w += v[h].w * fs;
     }
+  }
+#pragma unroll
+  for (int h = 0; h < kHeads; ++h) {
     const float inv = sh.merge_inv[h];
-    __nv_bfloat162 lo = __floats2bfloat162_rn(a.x * inv, a.y * inv);
-    __nv_bfloat162 hi = __floats2bfloat162_rn(a.z * inv, a.w * inv);
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a[h].x * inv, a[h].y * inv);
+    __nv_bfloat162 hi = __floats2bfloat162_rn(a[h].z * inv, a[h].w * inv);
     uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
     *reinterpret_cast<uint2*>(out + ((size_t)t * kHeads + h) * kCkv + c0) = packed;
   }
