@@ -83,6 +83,13 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
       : "memory");
 }
+// Ask the memory system to bring `bytes` (multiple of 16, 16-byte aligned) at `src` into L2.
+// Nothing is written to shared memory and nothing has to be waited for.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(src)),
+               "r"(bytes)
+               : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

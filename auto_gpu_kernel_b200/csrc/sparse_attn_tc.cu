@@ -23,8 +23,10 @@
 // CTA's range covers parts ("segments") of at most a few tokens; a token covered by several CTAs is
 // merged by whichever of them finishes last (atomic arrival counter, nobody waits).
 //
-// Warp roles (288 threads): warps 0-3 softmax + epilogue (TMEM lane quarter = warp), warp 4 MMA
-// issuer, warps 5-8 gather producers.  A producer warp instruction copies one 128-byte column
+// Warp roles (320 threads): warps 0-3 softmax + epilogue (TMEM lane quarter = warp), warp 4 MMA
+// issuer, warps 5-8 gather producers, warp 9 L2 prefetcher (it walks the index rows three tiles
+// ahead of the gather and issues one bulk L2 prefetch per selected row, so HBM latency is taken
+// by requests that need no shared-memory stage and the gather itself is served from L2).  A producer warp instruction copies one 128-byte column
 // block of four rows (8 lanes x 16 B per row, cp.async with zero-fill for masked rows) straight to
 // its swizzled place; a thread keeps its four row indices in registers, so the 36 copies of a
 // tile are address arithmetic with immediates only.  (The TMA tile::gather4 mode was measured
@@ -48,7 +50,8 @@ constexpr int kAtStageBytes = 9 * kAtBlockBytes;   // 73728
 constexpr int kAtQBlockBytes = kHeads * 128;       // 2048
 constexpr int kAtQBytes = 9 * kAtQBlockBytes;      // 18432
 constexpr int kAtPBytes = kHeads * 128;            // 2048
-constexpr int kAtThreads = 288;
+constexpr int kAtThreads = 320;
+constexpr int kAtPrefetchAhead = 3;                // tiles the L2 prefetcher runs ahead of the gather
 constexpr int kAtTmemCols = 256;
 constexpr int kAtSCol = 64;                        // O^T at 0..63; S^T buffer b at 64+64b (4 partials x 16)
 constexpr float kAtLog2e = 1.4426950408889634f;
@@ -68,6 +71,7 @@ struct AtShared {
   uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_free;
   uint32_t tmem_base;
   volatile int abort_flag;
+  volatile int tiles_gathered;  // progress of producer warp 0, paces the L2 prefetcher
   int is_last;
 };
 
@@ -234,6 +238,7 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
       }
       ptx::mbar_init(smem_u32(&sh.o_free), 4);
       sh.abort_flag = 0;
+      sh.tiles_gathered = 0;
       ptx::fence_barrier_init();
     }
     __syncwarp();
@@ -561,6 +566,27 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
         }
       }
       __syncwarp();
+    } else if (warp == 9) {
+      // =========================== L2 prefetcher ===========================
+      long t = w0 / tpt;
+      int j = (int)(w0 - t * tpt);
+      const int n_tiles = (int)(w1 - w0);
+      for (int i = 0; i < n_tiles && !sh.abort_flag; ++i) {
+        // stay at most kAtPrefetchAhead tiles ahead of the gather (bounded sleep-poll: this is only
+        // pacing, nothing depends on it)
+        for (int spin = 0; spin < 20000 && i >= sh.tiles_gathered + kAtPrefetchAhead && !sh.abort_flag; ++spin)
+          __nanosleep(100);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int k = j * kAtTile + half * 32 + lane;
+          const int slot = k < topk ? __ldg(indices + (size_t)t * index_stride + k) : -1;
+          if (slot >= 0 && slot < num_slots) {
+            ptx::bulk_prefetch_l2(ckv + (size_t)slot * kCkv, kCkv * 2);
+            ptx::bulk_prefetch_l2(kpe + (size_t)slot * kKpe, kKpe * 2);
+          }
+        }
+        if (++j == tpt) { j = 0; ++t; }
+      }
     } else {
       // =========================== gather producers (4 warps) ===========================
       const int pw = warp - 5;                       // producer warp 0..3
@@ -653,6 +679,7 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
         ptx::cp_async_arrive_noinc(smem_u32(&sh.kv_full[stage]));
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(smem_u32(&sh.kv_full[stage]));
+        if (pw == 0 && lane == 0) sh.tiles_gathered = i_tile + 1;
         t = t_next;
         j = j_next;
       }
