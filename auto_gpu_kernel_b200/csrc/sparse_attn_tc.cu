@@ -14,9 +14,7 @@
 //   O^T[512,16]      += V^T[512,64] . P^T          A = the SAME shared-memory tile read MN-major
 //                                                  (V is the 512-wide ckv part of the row);
 //                                                  B = P^T[16,64] bf16 written by the softmax warps
-// Shared-memory tile layout (one stage = 56 rows; three stages fit next to q and P^T, and the
-// M = 64 products simply run over 8 rows of the following block, whose results are masked / multiplied
-// by zero): nine [56 rows x 128 B] blocks (eight ckv column
+// Shared-memory tile layout (one stage = 64 rows): nine [64 rows x 128 B] blocks (eight ckv column
 // blocks, one kpe block), each in the canonical 128-byte-swizzle layout, so one gather feeds both
 // products.
 //
@@ -46,10 +44,9 @@
 
 namespace dsa {
 
-constexpr int kAtTile = 56;                        // gathered rows per tile (the MMAs run with M = 64)
-constexpr int kAtStages = 3;
-constexpr int kAtBlockBytes = kAtTile * 128;       // 7168 = 7 swizzle atoms
-constexpr int kAtStageBytes = 9 * kAtBlockBytes;   // 64512
+constexpr int kAtTile = 64;
+constexpr int kAtBlockBytes = kAtTile * 128;       // 8192
+constexpr int kAtStageBytes = 9 * kAtBlockBytes;   // 73728
 constexpr int kAtQBlockBytes = kHeads * 128;       // 2048
 constexpr int kAtQBytes = 9 * kAtQBlockBytes;      // 18432
 constexpr int kAtPBytes = kHeads * 128;            // 2048
@@ -63,14 +60,14 @@ constexpr uint32_t kIdescQK = ptx::idesc(ptx::kFmtBF16, ptx::kFmtBF16, false, fa
 constexpr uint32_t kIdescPV = ptx::idesc(ptx::kFmtBF16, ptx::kFmtBF16, true, false, 128, 16);
 
 struct AtShared {
-  int idx[kAtStages][64];
-  int live_w[kAtStages][4];      // per producer warp: the tile has at least one valid row
+  int idx[2][kAtTile];
+  int live_w[2][4];      // per producer warp: the tile has at least one valid row
   int need[4];
   float red[4][kHeads];
   float merge_f[32][kHeads];  // per-segment rescale factors of the token being merged
   float merge_inv[kHeads];
   int go[2];
-  uint64_t kv_full[kAtStages], kv_empty[kAtStages], q_full[1], q_empty[1];
+  uint64_t kv_full[2], kv_empty[2], q_full[2], q_empty[2];
   uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], o_free;
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -78,7 +75,7 @@ struct AtShared {
   int is_last;
 };
 
-constexpr size_t kAtDynBytes = 1024 + kAtStages * kAtStageBytes + kAtQBytes + 2 * kAtPBytes + sizeof(AtShared);
+constexpr size_t kAtDynBytes = 1024 + 2 * kAtStageBytes + 2 * kAtQBytes + 2 * kAtPBytes + sizeof(AtShared);
 
 struct AtPlan {
   int tiles_per_token;  // ceil(topk / 64)
@@ -141,11 +138,10 @@ size_t at_tc_workspace_bytes(int tokens, int topk, int sms) {
 // the outcome through shared memory: a timeout then makes all of them leave the loop together.
 // `bar2` (0 = none) is waited first; it only adds an acquire on a barrier that is already complete.
 __device__ __forceinline__ bool group_wait(AtShared& sh, int& toggle, bool leader, uint32_t bar2,
-                                           uint32_t parity2, uint32_t bar, uint32_t parity,
-                                           int32_t* status) {
+                                           uint32_t bar, uint32_t parity, int32_t* status) {
   if (leader) {
     bool ok = !sh.abort_flag;
-    if (ok && bar2) ok = ptx::mbar_wait(bar2, parity2);
+    if (ok && bar2) ok = ptx::mbar_wait(bar2, parity);
     if (ok) ok = ptx::mbar_wait(bar, parity);
     if (!ok && !sh.abort_flag) {
       sh.abort_flag = 1;
@@ -216,10 +212,10 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
   extern __shared__ unsigned char dyn_raw[];
   const uint32_t raw_addr = smem_u32(dyn_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
-  const uint32_t kv_addr = raw_addr + pad;                 // kAtStages stages
-  const uint32_t q_addr = kv_addr + kAtStages * kAtStageBytes;  // one q buffer
-  const uint32_t p_addr = q_addr + kAtQBytes;              // 2 P^T buffers
-  unsigned char* p_ptr = dyn_raw + pad + kAtStages * kAtStageBytes + kAtQBytes;
+  const uint32_t kv_addr = raw_addr + pad;                 // 2 stages
+  const uint32_t q_addr = kv_addr + 2 * kAtStageBytes;     // 2 q buffers
+  const uint32_t p_addr = q_addr + 2 * kAtQBytes;          // 2 P^T buffers
+  unsigned char* p_ptr = dyn_raw + pad + 2 * kAtStageBytes + 2 * kAtQBytes;
   AtShared& sh = *reinterpret_cast<AtShared*>(p_ptr + 2 * kAtPBytes);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -230,13 +226,11 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
 
   if (warp == 4) {
     if (lane == 0) {
-      for (int i = 0; i < kAtStages; ++i) {
+      for (int i = 0; i < 2; ++i) {
         ptx::mbar_init(smem_u32(&sh.kv_full[i]), 128 + 4);  // cp.async arrivals + 4 warp leaders
         ptx::mbar_init(smem_u32(&sh.kv_empty[i]), 4 + 1);   // softmax warps + MMA
-      }
-      ptx::mbar_init(smem_u32(&sh.q_full[0]), 128);
-      ptx::mbar_init(smem_u32(&sh.q_empty[0]), 1);
-      for (int i = 0; i < 2; ++i) {
+        ptx::mbar_init(smem_u32(&sh.q_full[i]), 128);
+        ptx::mbar_init(smem_u32(&sh.q_empty[i]), 1);
         ptx::mbar_init(smem_u32(&sh.s_full[i]), 1);
         ptx::mbar_init(smem_u32(&sh.s_empty[i]), 4);
         ptx::mbar_init(smem_u32(&sh.p_full[i]), 4);
@@ -251,9 +245,6 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
     ptx::tmem_alloc(smem_u32(&sh.tmem_base), kAtTmemCols);
     ptx::tmem_relinquish();
   }
-  // token columns kAtTile..63 of the P^T buffers are never written: they must read as zero
-  for (int i = tid; i < 2 * kAtPBytes / 4; i += kAtThreads) reinterpret_cast<uint32_t*>(p_ptr)[i] = 0u;
-  ptx::fence_proxy_async_smem();
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
@@ -268,7 +259,7 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
       const bool has_row = lane < 16;
       const int row = warp * 16 + (lane & 15);
       const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-      int toggle = 0, i_tile = 0, pl = 0, seg_live = 0, stage = 0, kphase = 0;
+      int toggle = 0, i_tile = 0, pl = 0, seg_live = 0;
       long cur_t = -1;
       float m_run[kHeads], l_part[kHeads];
       AtPartials part = at_carve(ws_raw, tokens, plan.segs_max);
@@ -283,10 +274,10 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
           cur_t = t;
         }
         const int sbuf = i_tile & 1, sphase = (i_tile >> 1) & 1;
-        if (!group_wait(sh, toggle, leader, smem_u32(&sh.kv_full[stage]), kphase,
-                        smem_u32(&sh.s_full[sbuf]), sphase, status)) break;
-        const bool live = (sh.live_w[stage][0] | sh.live_w[stage][1] | sh.live_w[stage][2] | sh.live_w[stage][3]) != 0;
-        const bool valid = has_row && row < kAtTile && sh.idx[stage][row] >= 0;
+        if (!group_wait(sh, toggle, leader, smem_u32(&sh.kv_full[sbuf]), smem_u32(&sh.s_full[sbuf]),
+                        sphase, status)) break;
+        const bool live = (sh.live_w[sbuf][0] | sh.live_w[sbuf][1] | sh.live_w[sbuf][2] | sh.live_w[sbuf][3]) != 0;
+        const bool valid = has_row && sh.idx[sbuf][row] >= 0;
         float x[kHeads];
         if (live) {
           ptx::tc_fence_after();
@@ -308,9 +299,8 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
         __syncwarp();
         if (lane == 0) {  // S^T buffer and the stage's index row have been read by this warp
           ptx::mbar_arrive(smem_u32(&sh.s_empty[sbuf]));
-          ptx::mbar_arrive(smem_u32(&sh.kv_empty[stage]));
+          ptx::mbar_arrive(smem_u32(&sh.kv_empty[sbuf]));
         }
-        if (++stage == kAtStages) { stage = 0; kphase ^= 1; }
         if (live) {
           bool need = false;
 #pragma unroll
@@ -340,7 +330,7 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
             if (seg_live > 0) {
               // PV of the previous live tile is complete when its P^T buffer has been released;
               // every earlier phase of that barrier is known complete (see the P^T write below).
-              if (!group_wait(sh, toggle, leader, 0, 0, smem_u32(&sh.p_empty[(pl - 1) & 1]),
+              if (!group_wait(sh, toggle, leader, 0, smem_u32(&sh.p_empty[(pl - 1) & 1]),
                               ((pl - 1) >> 1) & 1, status)) break;
               ptx::tc_fence_after();
 #pragma unroll
@@ -356,12 +346,10 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
               ptx::tc_fence_before();
             }
           }
-          // P^T buffer pl&1 was last read by the PV of live tile pl-2: wait for its release.  Every
-          // phase of this barrier is consumed here in order, which keeps the parity waits on
-          // "PV of tile pl-1 complete" (rescale above, epilogue below) unambiguous.
-          if (!group_wait(sh, toggle, leader, 0, 0, smem_u32(&sh.p_empty[pl & 1]), ((pl >> 1) & 1) ^ 1,
-                          status)) break;
-          if (has_row && row < kAtTile) {
+          // P^T buffer pl&1 was last read by the PV of live tile pl-2.  The MMA thread issued that PV
+          // before this tile's QK, and tcgen05.commit covers everything issued before it, so the
+          // s_full arrival observed above implies that PV is complete: the buffer is free.
+          if (has_row) {
             unsigned char* pb = p_ptr + (pl & 1) * kAtPBytes;
 #pragma unroll
             for (int h = 0; h < kHeads; ++h) {
@@ -382,7 +370,7 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
         if (j == tpt - 1 || w == w1 - 1) {
           // ------------------ end of this CTA's segment of token t ------------------
           if (seg_live > 0) {
-            if (!group_wait(sh, toggle, leader, 0, 0, smem_u32(&sh.p_empty[(pl - 1) & 1]),
+            if (!group_wait(sh, toggle, leader, 0, smem_u32(&sh.p_empty[(pl - 1) & 1]),
                             ((pl - 1) >> 1) & 1, status)) break;
             ptx::tc_fence_after();
           }
@@ -463,13 +451,13 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
       // Up to two PV products can be pending (tile i+1 scored before tile i is weighted).
       if (lane == 0) {
         const int n_tiles = (int)(w1 - w0);
-        int qk_i = 0, np = 0, seg_no = 0, qphase = 0, stage = 0, phase = 0;
+        int qk_i = 0, np = 0, seg_no = 0, qb = 0, qphase = 0;
         long cur_t = -1, t = w0 / tpt;
         int j = (int)(w0 - t * tpt);  // (t, j) of tile qk_i
         bool seg_first = true, ok = true;
         uint32_t q_lo = 0;
-        int pend_n = 0, pend_stage[kAtStages] = {0, 0, 0};
-        bool pend_first[kAtStages] = {false, false, false};
+        int pend_n = 0, pend_stage[2] = {0, 0};
+        bool pend_first[2] = {false, false};
         // constant descriptor halves: K-major (LBO 16, SBO 1024) and MN-major (LBO 8192, SBO 1024)
         const uint64_t dk = ptx::smem_desc_sw128(0, 16, 1024), dmn = ptx::smem_desc_sw128(0, kAtBlockBytes, 1024);
         const uint32_t k_hi = (uint32_t)(dk >> 32), k_lo0 = (uint32_t)dk;
@@ -501,8 +489,6 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
           ++np;
           pend_stage[0] = pend_stage[1];
           pend_first[0] = pend_first[1];
-          pend_stage[1] = pend_stage[2];
-          pend_first[1] = pend_first[2];
           --pend_n;
         };
         uint64_t idle_since = 0;
@@ -512,7 +498,7 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
             issue_pv();
             progressed = true;
           } else if (qk_i < n_tiles) {
-            const int sbuf = qk_i & 1, sphase = (qk_i >> 1) & 1;
+            const int stage = qk_i & 1, phase = (qk_i >> 1) & 1;
             if (t != cur_t) {
               // segment switch: everything of the previous segment must be issued and read first
               if (cur_t >= 0) {
@@ -520,26 +506,27 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
                   wait(sh.p_full[np & 1], (np >> 1) & 1);
                   if (ok) issue_pv();
                 }
-                ptx::tc_commit(smem_u32(&sh.q_empty[0]));
+                ptx::tc_commit(smem_u32(&sh.q_empty[qb ^ 1]));
                 wait(sh.o_free, seg_no & 1);  // epilogue of the previous segment has read O^T
                 ++seg_no;
               }
-              wait(sh.q_full[0], qphase);
+              wait(sh.q_full[qb], qphase);
               if (!ok) break;
-              q_lo = k_lo0 + (q_addr >> 4);
-              qphase ^= 1;
+              q_lo = k_lo0 + ((q_addr + qb * kAtQBytes) >> 4);
+              qb ^= 1;
+              if (qb == 0) qphase ^= 1;
               cur_t = t;
               seg_first = true;
               progressed = true;
-            } else if (pend_n < kAtStages && ptx::mbar_try_wait(smem_u32(&sh.kv_full[stage]), phase) &&
-                       ptx::mbar_try_wait(smem_u32(&sh.s_empty[sbuf]), sphase ^ 1)) {
+            } else if (pend_n < 2 && ptx::mbar_try_wait(smem_u32(&sh.kv_full[stage]), phase) &&
+                       ptx::mbar_try_wait(smem_u32(&sh.s_empty[stage]), phase ^ 1)) {
               ptx::fence_proxy_async_smem();  // cp.async-written tile / q -> visible to the MMA's reads
               const bool live = (sh.live_w[stage][0] | sh.live_w[stage][1] | sh.live_w[stage][2] |
                                  sh.live_w[stage][3]) != 0;
               if (live) {
                 ptx::tc_fence_after();
                 const uint32_t a_lo = k_lo0 + ((kv_addr + stage * kAtStageBytes) >> 4);
-                const uint32_t d0 = tmem_base + kAtSCol + sbuf * 64;
+                const uint32_t d0 = tmem_base + kAtSCol + stage * 64;
 #pragma unroll
                 for (int kb = 0; kb < 9; ++kb) {
 #pragma unroll
@@ -555,17 +542,16 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
                     ptx::tc_fence_after();
                   }
                 }
-                ptx::tc_commit(smem_u32(&sh.s_full[sbuf]));
+                ptx::tc_commit(smem_u32(&sh.s_full[stage]));
                 pend_stage[pend_n] = stage;
                 pend_first[pend_n] = seg_first;
                 ++pend_n;
                 seg_first = false;
               } else {
-                ptx::mbar_arrive(smem_u32(&sh.s_full[sbuf]));
+                ptx::mbar_arrive(smem_u32(&sh.s_full[stage]));
                 ptx::mbar_arrive(smem_u32(&sh.kv_empty[stage]));
               }
               ++qk_i;
-              if (++stage == kAtStages) { stage = 0; phase ^= 1; }
               if (++j == tpt) { j = 0; ++t; }
               progressed = true;
             }
@@ -593,7 +579,7 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           const int k = j * kAtTile + half * 32 + lane;
-          const int slot = (half * 32 + lane < kAtTile && k < topk) ? __ldg(indices + (size_t)t * index_stride + k) : -1;
+          const int slot = k < topk ? __ldg(indices + (size_t)t * index_stride + k) : -1;
           if (slot >= 0 && slot < num_slots) {
             ptx::bulk_prefetch_l2(ckv + (size_t)slot * kCkv, kCkv * 2);
             ptx::bulk_prefetch_l2(kpe + (size_t)slot * kKpe, kKpe * 2);
@@ -605,27 +591,28 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
       // =========================== gather producers (4 warps) ===========================
       const int pw = warp - 5;                       // producer warp 0..3
       const int sub = lane >> 3, ch = lane & 7;      // row inside a 4-row group, 16-byte chunk of a block
-      int i_tile = 0, qphase = 0, stage = 0, phase = 0;
+      int i_tile = 0, qb = 0, qphase = 0;
       long cur_t = -1;
       bool ok = true;
       auto load_indices = [&](long tt, int jj, int& a, int& b) {
         const int k0 = jj * kAtTile + lane, k1 = k0 + 32;
         a = k0 < topk ? __ldg(indices + (size_t)tt * index_stride + k0) : -1;
-        b = (lane + 32 < kAtTile && k1 < topk) ? __ldg(indices + (size_t)tt * index_stride + k1) : -1;
+        b = k1 < topk ? __ldg(indices + (size_t)tt * index_stride + k1) : -1;
       };
       long t = w0 / tpt;
       int j = (int)(w0 - t * tpt);
       int nv0, nv1;
       load_indices(t, j, nv0, nv1);
       for (long w = w0; w < w1; ++w, ++i_tile) {
+        const int stage = i_tile & 1, phase = (i_tile >> 1) & 1;
         if (t != cur_t) {
           if (lane == 0) {
-            ok = !sh.abort_flag && ptx::mbar_wait(smem_u32(&sh.q_empty[0]), qphase ^ 1);
+            ok = !sh.abort_flag && ptx::mbar_wait(smem_u32(&sh.q_empty[qb]), qphase ^ 1);
             if (!ok && !sh.abort_flag) { sh.abort_flag = 1; raise_status(status, DSA_STATUS_WAIT_TIMEOUT); }
           }
           ok = __shfl_sync(0xffffffffu, ok, 0);
           if (!ok) break;
-          const uint32_t qdst = q_addr;
+          const uint32_t qdst = q_addr + qb * kAtQBytes;
           const int ptid = pw * 32 + lane;
 #pragma unroll
           for (int it = 0; it < 9; ++it) {
@@ -634,9 +621,10 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
                                                : q_pe + ((size_t)(t * kHeads + h) * kKpe + (jj - 64) * 8);
             ptx::cp_async16(qdst + (jj >> 3) * kAtQBlockBytes + h * 128 + (((jj & 7) ^ (h & 7)) << 4), src, 16);
           }
-          ptx::cp_async_arrive_noinc(smem_u32(&sh.q_full[0]));
+          ptx::cp_async_arrive_noinc(smem_u32(&sh.q_full[qb]));
           cur_t = t;
-          qphase ^= 1;
+          qb ^= 1;
+          if (qb == 0) qphase ^= 1;
         }
         // the tile's 64 indices, two per lane (positions lane and lane+32); every warp reads all of
         // them so that each knows on its own whether the tile has any valid row.  They were
@@ -660,7 +648,7 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
         for (int gi = 0; gi < 4; ++gi) {
           const int r = 4 * (pw + 4 * gi) + sub;
           const int a = __shfl_sync(0xffffffffu, v0, r & 31), b = __shfl_sync(0xffffffffu, v1, r & 31);
-          slot[gi] = r < 32 ? a : (r < kAtTile ? b : -1);
+          slot[gi] = r < 32 ? a : b;
         }
         if (lane == 0) {
           ok = !sh.abort_flag && ptx::mbar_wait(smem_u32(&sh.kv_empty[stage]), phase ^ 1);
@@ -673,7 +661,6 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
 #pragma unroll
           for (int gi = 0; gi < 4; ++gi) {
             const int r = 4 * (pw + 4 * gi) + sub;
-            if (r >= kAtTile) continue;  // rows 56..63 of the M = 64 products are not part of the tile
             const int sl = slot[gi];
             const uint32_t nbytes = sl >= 0 ? 16u : 0u;
             const __nv_bfloat16* src_c = ckv + ((size_t)(sl >= 0 ? sl : 0) * kCkv + ch * 8);
@@ -693,7 +680,6 @@ sparse_attn_tc_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloa
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(smem_u32(&sh.kv_full[stage]));
         if (pw == 0 && lane == 0) sh.tiles_gathered = i_tile + 1;
-        if (++stage == kAtStages) { stage = 0; phase ^= 1; }
         t = t_next;
         j = j_next;
       }
