@@ -118,7 +118,15 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   // ---- sweep A: stage the row, min / max ------------------------------------------------------
   {
     float mn = INFINITY, mx = kSelFloor;
-    for (int i = tid; i < len; i += kSelThreads) {
+    const bool vec = (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
+    const int len4 = vec ? (len & ~3) : 0;
+    for (int i = tid * 4; i < len4; i += kSelThreads * 4) {  // 16-byte loads, all in flight at once
+      const float4 q = __ldg(reinterpret_cast<const float4*>(row + i));
+      if (staged) *reinterpret_cast<float4*>(row_s + i) = q;
+      mn = fminf(fminf(mn, fmaxf(q.x, kSelFloor)), fminf(fmaxf(q.y, kSelFloor), fminf(fmaxf(q.z, kSelFloor), fmaxf(q.w, kSelFloor))));
+      mx = fmaxf(fmaxf(mx, q.x), fmaxf(q.y, fmaxf(q.z, q.w)));
+    }
+    for (int i = len4 + tid; i < len; i += kSelThreads) {
       float v = __ldg(row + i);
       if (staged) row_s[i] = v;
       v = fmaxf(v, kSelFloor);
@@ -154,7 +162,15 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   };
 
   // ---- sweep B: histogram of the linear bins ---------------------------------------------------
-  for (int i = tid; i < len; i += kSelThreads) atomicAdd(&sh.hist[bin_of(value_at(i))], 1u);
+  // When the row is staged, its shared-memory copy is overwritten by the bin numbers: the later
+  // sweeps only compare bins, and the few boundary-bin elements re-read their score from L2.
+  int* bin_s = reinterpret_cast<int*>(row_s);
+  for (int i = tid; i < len; i += kSelThreads) {
+    const int bn = bin_of(value_at(i));
+    if (staged) bin_s[i] = bn;
+    atomicAdd(&sh.hist[bn], 1u);
+  }
+  auto bin_at = [&](int i) -> int { return staged ? bin_s[i] : bin_of(__ldg(row + i)); };
   __syncthreads();
   find_boundary_bin(sh, kSelBins, kTopK);
   const int edge = (int)sh.digit;          // boundary bin
@@ -171,7 +187,7 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   const int sweeps = (len + kSelThreads - 1) / kSelThreads;
   {
     uint32_t mine = 0;
-    for (int i = tid; i < len; i += kSelThreads) mine += bin_of(value_at(i)) > edge ? 1u : 0u;
+    for (int i = tid; i < len; i += kSelThreads) mine += bin_at(i) > edge ? 1u : 0u;
     uint32_t incl = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -183,14 +199,16 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
     base = __shfl_sync(0xffffffffu, base, 31);
     uint32_t pos = base + incl - mine;
     for (int i = tid; i < len; i += kSelThreads) {
-      const float v = value_at(i);
-      const int bin = bin_of(v);
+      const int bin = bin_at(i);
       if (bin > edge) {
         if (pos < (uint32_t)kTopK) out_row[pos] = slot_of(i);
         ++pos;
       } else if (few && bin == edge) {
         const uint32_t c = atomicAdd(&sh.cnt_cand, 1u);
-        if (c < (uint32_t)kSelCandCap) { sh.cand_key[c] = float_to_ordered(v); sh.cand_idx[c] = i; }
+        if (c < (uint32_t)kSelCandCap) {
+          sh.cand_key[c] = float_to_ordered(__ldg(row + i));
+          sh.cand_idx[c] = i;
+        }
       }
     }
   }
@@ -218,8 +236,8 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   }
 
   // ---- fallback: radix descent over the ordered keys of the boundary bin ------------------------
-  auto key_in_edge = [&](int i, uint32_t& key) -> bool {
-    const float v = value_at(i);
+  auto key_in_edge = [&](int i, uint32_t& key) -> bool {  // the staged copy now holds bins
+    const float v = __ldg(row + i);
     key = float_to_ordered(v);
     return bin_of(v) == edge;
   };
