@@ -32,6 +32,9 @@ SIGNATURES = {
     "dsa_sparse_attn_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int]),
     "dsa_sparse_attn": (_c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _c_float, _ptr, _ptr,
                                  _c_int, _c_int, _c_int, _c_i64, _ptr, _c_size, _ptr, _ptr]),
+    "dsa_sparse_attn_tcgen05": (_c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _c_float, _ptr,
+                                         _ptr, _c_int, _c_int, _c_int, _c_i64, _ptr, _c_size,
+                                         _ptr, _ptr]),
     "dsa_sparse_attn_cuda_core": (_c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _c_float, _ptr,
                                            _ptr, _c_int, _c_int, _c_int, _c_i64, _ptr, _c_size,
                                            _ptr, _ptr]),

@@ -20,6 +20,9 @@ cudaError_t launch_sparse_attn_tc(const void*, const void*, const void*, const v
                                   const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
                                   void*, int32_t*, cudaStream_t);
 size_t at_tc_workspace_bytes_auto(int tokens, int topk);
+cudaError_t launch_sparse_attn_mma(const void*, const void*, const void*, const void*,
+                                   const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
+                                   void*, int32_t*, cudaStream_t);
 int att_pick_splits(int tokens, int topk);
 size_t att_workspace_bytes(int tokens, int splits);
 }  // namespace dsa
@@ -155,9 +158,14 @@ static int attn_impl(const void* q_nope, const void* q_pe, const void* ckv, cons
                                                          topk, num_slots, splits, workspace,
                                                          status_dev, s));
   }
-  return static_cast<int>(dsa::launch_sparse_attn_tc(q_nope, q_pe, ckv, kpe, sparse_indices,
-                                                     index_stride, sm_scale, out, lse, tokens, topk,
-                                                     num_slots, workspace, status_dev, s));
+  if (variant == 2) {
+    return static_cast<int>(dsa::launch_sparse_attn_tc(q_nope, q_pe, ckv, kpe, sparse_indices,
+                                                       index_stride, sm_scale, out, lse, tokens,
+                                                       topk, num_slots, workspace, status_dev, s));
+  }
+  return static_cast<int>(dsa::launch_sparse_attn_mma(q_nope, q_pe, ckv, kpe, sparse_indices,
+                                                      index_stride, sm_scale, out, lse, tokens, topk,
+                                                      num_slots, workspace, status_dev, s));
 }
 
 int dsa_sparse_attn(const void* q_nope, const void* q_pe, const void* ckv, const void* kpe,
@@ -175,6 +183,15 @@ int dsa_sparse_attn_cuda_core(const void* q_nope, const void* q_pe, const void* 
                               int32_t* status_dev, void* stream) {
   return attn_impl(q_nope, q_pe, ckv, kpe, sparse_indices, index_stride, sm_scale, out, lse, tokens,
                    heads, topk, num_slots, workspace, workspace_bytes, status_dev, stream, 1);
+}
+
+int dsa_sparse_attn_tcgen05(const void* q_nope, const void* q_pe, const void* ckv, const void* kpe,
+                            const int32_t* sparse_indices, int64_t index_stride, float sm_scale,
+                            void* out, float* lse, int tokens, int heads, int topk,
+                            int64_t num_slots, void* workspace, size_t workspace_bytes,
+                            int32_t* status_dev, void* stream) {
+  return attn_impl(q_nope, q_pe, ckv, kpe, sparse_indices, index_stride, sm_scale, out, lse, tokens,
+                   heads, topk, num_slots, workspace, workspace_bytes, status_dev, stream, 2);
 }
 
 }  // extern "C"

@@ -1,0 +1,391 @@
+// Sparse MLA attention over the selected rows, decode shape (16 heads per token).
+//
+//   logit[h,k] = (q_nope[h].ckv[idx[k]] + q_pe[h].kpe[idx[k]]) * sm_scale      idx == -1 -> masked
+//   lse[h]     = log2( sum_k e^{logit[h,k]} )          out[h] = softmax_k(logit[h,:]) @ ckv[idx[:]]
+// (reference arithmetic: sparse_baseline.py:18-45; kernels this replaces: sparse_fused.py:23-285 and
+//  the Gluon _dsa_decode_gluon of archive/fable/dsa_sparse_attention_*.py:77-433).
+//
+// Why warp-level MMA here: with 16 heads the tcgen05 formulation has N = 16, and a tcgen05.mma costs
+// max(45.6, N/2) cycles whatever M is -- 52 instructions per 64-row tile, 3.0-4.7 k cycles, more than
+// the HBM time of the tile.  mma.sync m16n8k16 was measured on this part at 2.0 cycles per
+// instruction per SM (2048 MAC/clk); M = 16 is exactly the head count, so a tile is 544
+// instructions = 1.1 k cycles, and the kernel is bound by the gather as it should be.
+//
+// Structure (one CTA of 8 warps per SM, no warp specialisation, no mbarrier, nothing that spins):
+//   * three 64-row stages in shared memory, filled by cp.async 16-byte copies issued by all warps
+//     two tiles ahead; a tile is nine [64 rows x 128 B] blocks (8 ckv column blocks + kpe) with the
+//     16-byte chunks of a row XOR-swizzled by (row & 7), so both ldmatrix patterns below are
+//     conflict-free; masked rows (-1) are zero-filled;
+//   * S[16 heads, 64 rows] = Q.K^T: warp w owns rows 8w..8w+7; q lives in registers as the 36
+//     A fragments of the token (loaded once per token), K fragments come from ldmatrix.x4;
+//   * online softmax in base 2 with a lazily refreshed running max (refreshed, and O rescaled in
+//     registers, only when a logit exceeds it by more than 2^8); P^T goes through 2 KB of shared
+//     memory so that every warp sees all 64 rows;
+//   * O[16 heads, 512] += P.V: warp w owns output columns 64w..64w+63 = column block w of the same
+//     tile, read with ldmatrix.x4.trans; accumulators stay in registers;
+//   * the (token, tile) sequence is cut into equal contiguous ranges, one per CTA; tokens covered by
+//     several CTAs leave partials in the workspace and are merged by the CTA that arrives last.
+#include <cuda_pipeline_primitives.h>
+
+#include "attn_plan.cuh"
+#include "common.cuh"
+#include "ptx.cuh"
+#include "tmap.cuh"
+
+namespace dsa {
+
+constexpr int kMmStages = 3;
+constexpr int kMmBlockBytes = kAtTile * 128;        // 8192
+constexpr int kMmStageBytes = 9 * kMmBlockBytes;    // 73728
+constexpr int kMmThreads = 256;
+constexpr int kMmPBytes = kHeads * 128;             // P^T [16 heads][64 rows] bf16
+constexpr float kMmLog2e = 1.4426950408889634f;
+constexpr float kMmRescaleGap = 8.f;
+
+struct MmShared {
+  int idx[kMmStages][kAtTile];
+  int live[kMmStages];
+  float red[8][kHeads];
+  float merge_f[32][kHeads];
+  float merge_inv[kHeads];
+  int is_last;
+};
+
+constexpr size_t kMmDynBytes = 128 + kMmStages * kMmStageBytes + kMmPBytes + sizeof(MmShared);
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+// D[16x8] += A[16x16] . B[16x8], bf16 inputs, fp32 accumulate.
+__device__ __forceinline__ void hmma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf162(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Merge of the per-segment partials of one token by the 256 threads of the last-arriving CTA:
+// threads 0..15 turn the segments' (m, l) into rescale factors, then each thread owns two output
+// columns and walks the 16 heads with all loads of a segment in flight.
+__device__ void mm_merge_segments(MmShared& sh, const AtPartials& w, int t, int n_seg, int segs_max,
+                                  __nv_bfloat16* out, float* lse, int tid) {
+  if (tid < kHeads) {
+    const int h = tid;
+    float mx = -INFINITY;
+    for (int s = 0; s < n_seg; ++s) mx = fmaxf(mx, w.m[((size_t)t * segs_max + s) * kHeads + h]);
+    float lsum = 0.f;
+    for (int s = 0; s < n_seg; ++s) {
+      const size_t o = ((size_t)t * segs_max + s) * kHeads + h;
+      const float ms = w.m[o];
+      const float fs = (ms == -INFINITY) ? 0.f : exp2f(ms - mx);
+      sh.merge_f[s][h] = fs;
+      lsum += w.l[o] * fs;
+    }
+    sh.merge_inv[h] = lsum > 0.f ? 1.f / lsum : 0.f;
+    lse[(size_t)t * kHeads + h] = lsum > 0.f ? mx + log2f(lsum) : -INFINITY;
+  }
+  __syncthreads();
+  const int c0 = tid * 2;
+  float2 a[kHeads];
+#pragma unroll
+  for (int h = 0; h < kHeads; ++h) a[h] = make_float2(0.f, 0.f);
+  for (int s = 0; s < n_seg; ++s) {
+    const float* base = w.acc + ((size_t)t * segs_max + s) * kHeads * kCkv + c0;
+    float2 v[kHeads];
+#pragma unroll
+    for (int h = 0; h < kHeads; ++h) v[h] = *reinterpret_cast<const float2*>(base + h * kCkv);
+#pragma unroll
+    for (int h = 0; h < kHeads; ++h) {
+      const float fs = sh.merge_f[s][h];
+      a[h].x += v[h].x * fs;
+      a[h].y += v[h].y * fs;
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < kHeads; ++h) {
+    const float inv = sh.merge_inv[h];
+    *reinterpret_cast<uint32_t*>(out + ((size_t)t * kHeads + h) * kCkv + c0) = pack_bf162(a[h].x * inv, a[h].y * inv);
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kMmThreads, 1)
+sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloat16* __restrict__ q_pe,
+                       const __nv_bfloat16* __restrict__ ckv, const __nv_bfloat16* __restrict__ kpe,
+                       const int32_t* __restrict__ indices, int64_t index_stride, float scale_log2,
+                       __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int tokens, int topk,
+                       int64_t num_slots, AtPlan plan, void* ws_raw, int32_t* status) {
+  extern __shared__ unsigned char dyn_raw[];
+  const uint32_t raw_addr = smem_u32(dyn_raw);
+  const uint32_t pad = (128u - (raw_addr & 127u)) & 127u;
+  const uint32_t kv_addr = raw_addr + pad;
+  const uint32_t p_addr = kv_addr + kMmStages * kMmStageBytes;
+  unsigned char* p_ptr = dyn_raw + pad + kMmStages * kMmStageBytes;
+  MmShared& sh = *reinterpret_cast<MmShared*>(p_ptr + kMmPBytes);
+
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int tpt = plan.tiles_per_token;
+  const long total = (long)tokens * tpt;
+  const long w0 = (long)blockIdx.x * plan.per_cta;
+  const long w1 = w0 + plan.per_cta < total ? w0 + plan.per_cta : total;
+  const int n = (int)(w1 - w0);
+  if (n <= 0) return;
+  AtPartials part = at_carve(ws_raw, tokens, plan.segs_max);
+
+  // ---------------- gather issue: tile `issued` goes to stage issued % 3 ------------------------
+  long ti = w0 / tpt;                 // (token, tile-in-token) of the next tile to issue
+  int ji = (int)(w0 - ti * tpt);
+  int issued = 0, nv0 = -1, nv1 = -1; // its 64 indices, two per lane, requested one tile ahead
+  auto load_indices = [&](long tt, int jj, int& a, int& b) {
+    const int k0 = jj * kAtTile + lane, k1 = k0 + 32;
+    a = k0 < topk ? __ldg(indices + (size_t)tt * index_stride + k0) : -1;
+    b = k1 < topk ? __ldg(indices + (size_t)tt * index_stride + k1) : -1;
+  };
+  load_indices(ti, ji, nv0, nv1);
+  const int sub = lane >> 3, ch = lane & 7;  // row inside a 4-row group, 16-byte chunk of a 128-byte block
+  auto issue_tile = [&]() {
+    if (issued < n) {
+      const int s = issued % kMmStages;
+      int v0 = nv0, v1 = nv1;
+      if (++ji == tpt) { ji = 0; ++ti; }
+      if (issued + 1 < n) load_indices(ti, ji, nv0, nv1);
+      if (v0 >= num_slots || v1 >= num_slots) {
+        raise_status(status, DSA_STATUS_BAD_SLOT);
+        if (v0 >= num_slots) v0 = -1;
+        if (v1 >= num_slots) v1 = -1;
+      }
+      if (v0 < 0) v0 = -1;
+      if (v1 < 0) v1 = -1;
+      const bool live = __any_sync(0xffffffffu, v0 >= 0 || v1 >= 0);
+      const uint32_t dst0 = kv_addr + s * kMmStageBytes;
+#pragma unroll
+      for (int gi = 0; gi < 2; ++gi) {       // this warp copies row groups w and w + 8
+        const int r = 4 * (w + 8 * gi) + sub;
+        const int a = __shfl_sync(0xffffffffu, v0, r & 31), b = __shfl_sync(0xffffffffu, v1, r & 31);
+        const int sl = r < 32 ? a : b;
+        if (live) {
+          const uint32_t nbytes = sl >= 0 ? 16u : 0u;
+          const __nv_bfloat16* src_c = ckv + ((size_t)(sl >= 0 ? sl : 0) * kCkv + ch * 8);
+          const __nv_bfloat16* src_p = kpe + ((size_t)(sl >= 0 ? sl : 0) * kKpe + ch * 8);
+          const uint32_t dst = dst0 + r * 128 + ((ch ^ (r & 7)) << 4);
+#pragma unroll
+          for (int kb = 0; kb < 8; ++kb) ptx::cp_async16(dst + kb * kMmBlockBytes, src_c + kb * 64, nbytes);
+          ptx::cp_async16(dst + 8 * kMmBlockBytes, src_p, nbytes);
+        }
+        if (ch == 0) sh.idx[s][r] = sl;
+      }
+      if (tid == 0) sh.live[s] = live ? 1 : 0;
+    }
+    cp_async_commit();  // always: keeps "all but the newest group" == "tile i has landed"
+    ++issued;
+  };
+  issue_tile();
+  issue_tile();
+
+  // ---------------- per-token state --------------------------------------------------------------
+  uint32_t qa[36][4];          // A fragments of q: k-step ks covers columns 16 ks .. 16 ks + 15
+  float o[8][4];               // O[heads g / g+8][columns 64 w + 8 n + 2 t4, +1]
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  long t = w0 / tpt, cur_t = -1;
+  int j = (int)(w0 - t * tpt) - 1;
+
+  for (int i = 0; i < n; ++i) {
+    if (++j == tpt) { j = 0; ++t; }
+    if (t != cur_t) {
+      const __nv_bfloat16* qn0 = q_nope + (size_t)(t * kHeads + g) * kCkv;
+      const __nv_bfloat16* qn1 = qn0 + 8 * kCkv;
+      const __nv_bfloat16* qp0 = q_pe + (size_t)(t * kHeads + g) * kKpe;
+      const __nv_bfloat16* qp1 = qp0 + 8 * kKpe;
+#pragma unroll
+      for (int ks = 0; ks < 36; ++ks) {
+        const int c = (ks < 32 ? ks * 16 : (ks - 32) * 16) + 2 * t4;
+        const __nv_bfloat16* r0 = ks < 32 ? qn0 : qp0;
+        const __nv_bfloat16* r1 = ks < 32 ? qn1 : qp1;
+        qa[ks][0] = __ldg(reinterpret_cast<const uint32_t*>(r0 + c));
+        qa[ks][1] = __ldg(reinterpret_cast<const uint32_t*>(r1 + c));
+        qa[ks][2] = __ldg(reinterpret_cast<const uint32_t*>(r0 + c + 8));
+        qa[ks][3] = __ldg(reinterpret_cast<const uint32_t*>(r1 + c + 8));
+      }
+#pragma unroll
+      for (int nn = 0; nn < 8; ++nn) o[nn][0] = o[nn][1] = o[nn][2] = o[nn][3] = 0.f;
+      m0 = m1 = -INFINITY;
+      l0 = l1 = 0.f;
+      cur_t = t;
+    }
+    cp_async_wait_group<1>();   // tile i has landed (only the newest group, tile i+1, may be pending)
+    __syncthreads();            // ... for every thread; and everyone is done with tile i-1
+    issue_tile();               // tile i+2 -> the stage tile i-1 used
+    const int s = i % kMmStages;
+    if (sh.live[s]) {
+      const uint32_t sa = kv_addr + s * kMmStageBytes;
+      // ---- S = Q . K^T for rows 8w .. 8w+7 -----------------------------------------------------
+      float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+      {
+        const int row_l = 8 * w + (lane & 7);
+        const uint32_t brow = sa + row_l * 128;
+        const int rx = row_l & 7, quad = lane >> 3;
+#pragma unroll
+        for (int kb = 0; kb < 9; ++kb) {
+#pragma unroll
+          for (int kk = 0; kk < 2; ++kk) {
+            uint32_t r0, r1, r2, r3;
+            ldsm_x4(brow + kb * kMmBlockBytes + (((kk * 4 + quad) ^ rx) << 4), r0, r1, r2, r3);
+            hmma_16816(sacc, qa[kb * 4 + 2 * kk], r0, r1);
+            hmma_16816(sacc, qa[kb * 4 + 2 * kk + 1], r2, r3);
+          }
+        }
+      }
+      const int ra = 8 * w + 2 * t4;
+      const bool va = sh.idx[s][ra] >= 0, vb = sh.idx[s][ra + 1] >= 0;
+      const float x0 = va ? sacc[0] * scale_log2 : -INFINITY, x1 = vb ? sacc[1] * scale_log2 : -INFINITY;
+      const float x2 = va ? sacc[2] * scale_log2 : -INFINITY, x3 = vb ? sacc[3] * scale_log2 : -INFINITY;
+      const bool need = fmaxf(x0, x1) > m0 + kMmRescaleGap || fmaxf(x2, x3) > m1 + kMmRescaleGap;
+      if (__syncthreads_or(need)) {
+        // refresh the running max of every head over the tile, rescale the accumulators
+        float v0 = fmaxf(x0, x1), v1 = fmaxf(x2, x3);
+        v0 = fmaxf(v0, __shfl_xor_sync(0xffffffffu, v0, 1));
+        v0 = fmaxf(v0, __shfl_xor_sync(0xffffffffu, v0, 2));
+        v1 = fmaxf(v1, __shfl_xor_sync(0xffffffffu, v1, 1));
+        v1 = fmaxf(v1, __shfl_xor_sync(0xffffffffu, v1, 2));
+        if (t4 == 0) { sh.red[w][g] = v0; sh.red[w][g + 8] = v1; }
+        __syncthreads();
+        float mx0 = sh.red[0][g], mx1 = sh.red[0][g + 8];
+#pragma unroll
+        for (int ww = 1; ww < 8; ++ww) { mx0 = fmaxf(mx0, sh.red[ww][g]); mx1 = fmaxf(mx1, sh.red[ww][g + 8]); }
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        const float c0 = n0 == -INFINITY ? 1.f : exp2f(m0 - n0), c1 = n1 == -INFINITY ? 1.f : exp2f(m1 - n1);
+#pragma unroll
+        for (int nn = 0; nn < 8; ++nn) { o[nn][0] *= c0; o[nn][1] *= c0; o[nn][2] *= c1; o[nn][3] *= c1; }
+        l0 *= c0; l1 *= c1;
+        m0 = n0; m1 = n1;
+      }
+      {
+        const float u0 = m0 == -INFINITY ? 0.f : m0, u1 = m1 == -INFINITY ? 0.f : m1;
+        const float p0 = exp2f(x0 - u0), p1 = exp2f(x1 - u0), p2 = exp2f(x2 - u1), p3 = exp2f(x3 - u1);
+        l0 += p0 + p1;
+        l1 += p2 + p3;
+        // P^T[head][row]: rows 8w..8w+7 are 16-byte chunk w of the head's 128-byte line
+        *reinterpret_cast<uint32_t*>(p_ptr + g * 128 + ((w ^ (g & 7)) << 4) + t4 * 4) = pack_bf162(p0, p1);
+        *reinterpret_cast<uint32_t*>(p_ptr + (g + 8) * 128 + ((w ^ (g & 7)) << 4) + t4 * 4) = pack_bf162(p2, p3);
+      }
+      __syncthreads();
+      // ---- O += P . V for columns 64w .. 64w+63 (column block w of the tile) ---------------------
+      {
+        const int hrow = (lane & 7) + ((lane >> 3) & 1) * 8, half = lane >> 4;
+        const uint32_t pa = p_addr + hrow * 128;
+        const uint32_t vbase = sa + w * kMmBlockBytes;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          uint32_t a[4];
+          ldsm_x4(pa + (((ks * 2 + half) ^ (hrow & 7)) << 4), a[0], a[1], a[2], a[3]);
+          const int vrow = ks * 16 + hrow;
+          const uint32_t va_addr = vbase + vrow * 128;
+#pragma unroll
+          for (int np = 0; np < 4; ++np) {
+            uint32_t r0, r1, r2, r3;
+            ldsm_x4_trans(va_addr + (((np * 2 + half) ^ (vrow & 7)) << 4), r0, r1, r2, r3);
+            hmma_16816(o[2 * np], a, r0, r1);
+            hmma_16816(o[2 * np + 1], a, r2, r3);
+          }
+        }
+      }
+    }
+    if (j == tpt - 1 || i == n - 1) {
+      // ------------------ end of this CTA's segment of token t ------------------------------------
+      float s0 = l0, s1 = l1;
+      s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+      s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+      s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+      s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+      __syncthreads();  // sh.red may still be read by a slow warp of a refresh above
+      if (t4 == 0) { sh.red[w][g] = s0; sh.red[w][g + 8] = s1; }
+      __syncthreads();
+      float lt0 = 0.f, lt1 = 0.f;
+#pragma unroll
+      for (int ww = 0; ww < 8; ++ww) { lt0 += sh.red[ww][g]; lt1 += sh.red[ww][g + 8]; }
+      const long first_tile = t * tpt, last_tile = first_tile + tpt - 1;
+      const int cta_first = (int)(first_tile / plan.per_cta), cta_last = (int)(last_tile / plan.per_cta);
+      const int n_seg = cta_last - cta_first + 1, seg = (int)blockIdx.x - cta_first;
+      const int col = 64 * w + 2 * t4;
+      if (n_seg == 1) {
+        const float i0 = lt0 > 0.f ? 1.f / lt0 : 0.f, i1 = lt1 > 0.f ? 1.f / lt1 : 0.f;
+        __nv_bfloat16* oa = out + ((size_t)t * kHeads + g) * kCkv + col;
+        __nv_bfloat16* ob = oa + 8 * kCkv;
+#pragma unroll
+        for (int nn = 0; nn < 8; ++nn) {
+          *reinterpret_cast<uint32_t*>(oa + 8 * nn) = pack_bf162(o[nn][0] * i0, o[nn][1] * i0);
+          *reinterpret_cast<uint32_t*>(ob + 8 * nn) = pack_bf162(o[nn][2] * i1, o[nn][3] * i1);
+        }
+        if (w == 0 && t4 == 0) {
+          lse[(size_t)t * kHeads + g] = lt0 > 0.f ? m0 + log2f(lt0) : -INFINITY;
+          lse[(size_t)t * kHeads + g + 8] = lt1 > 0.f ? m1 + log2f(lt1) : -INFINITY;
+        }
+      } else {
+        float* pa = part.acc + (((size_t)t * plan.segs_max + seg) * kHeads + g) * kCkv + col;
+        float* pb = pa + 8 * kCkv;
+#pragma unroll
+        for (int nn = 0; nn < 8; ++nn) {
+          *reinterpret_cast<float2*>(pa + 8 * nn) = make_float2(o[nn][0], o[nn][1]);
+          *reinterpret_cast<float2*>(pb + 8 * nn) = make_float2(o[nn][2], o[nn][3]);
+        }
+        if (w == 0 && t4 == 0) {
+          const size_t base = ((size_t)t * plan.segs_max + seg) * kHeads;
+          part.m[base + g] = lt0 > 0.f ? m0 : -INFINITY;
+          part.l[base + g] = lt0;
+          part.m[base + g + 8] = lt1 > 0.f ? m1 : -INFINITY;
+          part.l[base + g + 8] = lt1;
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+          const int old = atomicAdd(&part.counters[t], 1);
+          sh.is_last = old == n_seg - 1;
+          if (sh.is_last) part.counters[t] = 0;  // ready for the next call
+        }
+        __syncthreads();
+        if (sh.is_last) {
+          __threadfence();
+          mm_merge_segments(sh, part, (int)t, n_seg, plan.segs_max, out, lse, tid);
+        }
+      }
+    }
+  }
+  cp_async_wait_group<0>();
+}
+
+cudaError_t launch_sparse_attn_mma(const void* q_nope, const void* q_pe, const void* ckv,
+                                   const void* kpe, const int32_t* indices, int64_t index_stride,
+                                   float sm_scale, void* out, float* lse, int tokens, int topk,
+                                   int64_t num_slots, void* ws, int32_t* status, cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(sparse_attn_mma_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmDynBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  const AtPlan plan = at_make_plan(tokens, topk, sm_count());
+  sparse_attn_mma_kernel<<<plan.grid, kMmThreads, kMmDynBytes, stream>>>(
+      static_cast<const __nv_bfloat16*>(q_nope), static_cast<const __nv_bfloat16*>(q_pe),
+      static_cast<const __nv_bfloat16*>(ckv), static_cast<const __nv_bfloat16*>(kpe), indices,
+      index_stride, sm_scale * kMmLog2e, static_cast<__nv_bfloat16*>(out), lse, tokens, topk,
+      num_slots, plan, ws, status);
+  return cudaGetLastError();
+}
+
+}  // namespace dsa

@@ -20,7 +20,8 @@ KPE = 64
 
 def kernel(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale, output, lse, variant=0):
     """Write attention output and base-2 LSE in place; enqueued on the current stream, returns None.
-    `variant` 0 = tcgen05 kernel, 1 = CUDA-core cross-check kernel (not part of the reference
+    `variant` 0 = default (warp-level mma.sync) kernel, 1 = CUDA-core cross-check kernel, 2 =
+    tcgen05/TMEM kernel (not part of the reference
     signature; positional callers never pass it)."""
     if not q_nope.is_cuda:
         raise RuntimeError("dsa sparse attention: CUDA tensors required (this operator has no CPU path)")
@@ -58,7 +59,7 @@ def kernel(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale, output,
     need = lib.dsa_sparse_attn_workspace_bytes(tokens, HEADS, topk)
     ws = workspace.get(dev, "attention", need)
     with torch.cuda.device(dev):
-        fn = lib.dsa_sparse_attn if variant == 0 else lib.dsa_sparse_attn_cuda_core
+        fn = (lib.dsa_sparse_attn, lib.dsa_sparse_attn_cuda_core, lib.dsa_sparse_attn_tcgen05)[variant]
         rc = fn(
             q_nope.data_ptr(), q_pe.data_ptr(), ckv_cache.data_ptr(), kpe_cache.data_ptr(),
             sparse_indices.data_ptr(), sparse_indices.stride(0), float(sm_scale),

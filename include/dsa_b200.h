@@ -115,8 +115,18 @@ int dsa_sparse_attn(const void* q_nope, const void* q_pe, const void* ckv, const
                     void* out, float* lse, int tokens, int heads, int topk, int64_t num_slots,
                     void* workspace, size_t workspace_bytes, int32_t* status_dev, void* stream);
 
-/* Same contract as dsa_sparse_attn, computed with plain CUDA-core FMAs instead of tcgen05: an
- * on-device cross-check at sizes where the CPU oracle is slow.  Same reference interface. */
+/* Same contract as dsa_sparse_attn (which runs the warp-level mma.sync kernel: with 16 heads it is
+ * the fastest formulation on B200), computed with the tcgen05/TMEM kernel that issues the
+ * products transposed (heads as N = 16).  Same reference interface; kept selectable because it is
+ * the formulation that wins once more heads share a gathered row. */
+int dsa_sparse_attn_tcgen05(const void* q_nope, const void* q_pe, const void* ckv, const void* kpe,
+                            const int32_t* sparse_indices, int64_t index_stride, float sm_scale,
+                            void* out, float* lse, int tokens, int heads, int topk,
+                            int64_t num_slots, void* workspace, size_t workspace_bytes,
+                            int32_t* status_dev, void* stream);
+
+/* Same contract as dsa_sparse_attn, computed with plain CUDA-core FMAs: an on-device cross-check
+ * at sizes where the CPU oracle is slow.  Same reference interface. */
 int dsa_sparse_attn_cuda_core(const void* q_nope, const void* q_pe, const void* ckv,
                               const void* kpe, const int32_t* sparse_indices, int64_t index_stride,
                               float sm_scale, void* out, float* lse, int tokens, int heads, int topk,

@@ -9,7 +9,7 @@ from helpers import assert_attention_close, load_attention_golden
 pytestmark = pytest.mark.gpu
 
 
-VARIANTS = pytest.mark.parametrize("variant", [1, 0], ids=["cuda_core", "tcgen05"])
+VARIANTS = pytest.mark.parametrize("variant", [1, 0, 2], ids=["cuda_core", "mma_sync", "tcgen05"])
 
 
 @VARIANTS
