@@ -11,15 +11,13 @@
 // instruction per SM (2048 MAC/clk); M = 16 is exactly the head count, so a tile is 544
 // instructions = 1.1 k cycles, and the kernel is bound by the gather as it should be.
 //
-// Structure (one CTA of 8 warps per SM, no warp specialisation):
-//   * three 64-row stages in shared memory.  A row is stored as it is in HBM (1024 B ckv then
-//     128 B kpe) at a pitch of 1168 B (73 x 16 B, odd), which makes both ldmatrix patterns below
-//     conflict-free without any swizzle -- so a row is fetched by two plain bulk copies
-//     (cp.async.bulk 1024 B + 128 B) straight from the flat caches, issued two tiles ahead by the
-//     lanes of warp 0 (two rows per lane) and completing on an mbarrier per stage.  The bulk
-//     engine keeps the load/store unit free for the ldmatrix traffic: with 16-byte cp.async the
-//     gather (about 27 B/clk/SM through the LSU) and the fragment loads serialised on that unit.
-//     Masked rows (-1) are zero-filled with ordinary stores;
+// Structure (one CTA of 8 warps per SM, no warp specialisation, no mbarrier, nothing that spins):
+//   * three 64-row stages in shared memory, filled by cp.async 16-byte copies issued by all warps
+//     two tiles ahead; a tile is nine [64 rows x 128 B] blocks (8 ckv column blocks + kpe) with the
+//     16-byte chunks of a row XOR-swizzled by (row & 7), so both ldmatrix patterns below are
+//     conflict-free; masked rows (-1) are zero-filled.  (Fetching rows with cp.async.bulk, 1024 B +
+//     128 B per row into linear padded rows, was measured at 92.7 us for the headline shape against
+//     50.5 us for these 16-byte copies: the bulk engine costs ~70 cycles per request.);
 //   * S[16 heads, 64 rows] = Q.K^T: warp w owns rows 8w..8w+7; q lives in registers as the 36
 //     A fragments of the token (loaded once per token), K fragments come from ldmatrix.x4;
 //   * online softmax in base 2 with a lazily refreshed running max (refreshed, and O rescaled in
@@ -39,9 +37,8 @@
 namespace dsa {
 
 constexpr int kMmStages = 3;
-constexpr int kMmPitch = 1168;                       // bytes between rows of a stage (1152 data + 16)
-constexpr int kMmRowBytes = 1152;
-constexpr int kMmStageBytes = kAtTile * kMmPitch;   // 74752
+constexpr int kMmBlockBytes = kAtTile * 128;        // 8192
+constexpr int kMmStageBytes = 9 * kMmBlockBytes;    // 73728
 constexpr int kMmThreads = 256;
 constexpr int kMmPBytes = kHeads * 128;             // P^T [16 heads][64 rows] bf16
 constexpr float kMmLog2e = 1.4426950408889634f;
@@ -49,8 +46,7 @@ constexpr float kMmRescaleGap = 8.f;
 
 struct MmShared {
   int idx[kMmStages][kAtTile];
-  int live[kMmStages];      // the tile has at least one valid row
-  uint64_t full[kMmStages];
+  int live[kMmStages];
   float red[8][kHeads];
   float merge_f[32][kHeads];
   float merge_inv[kHeads];
@@ -154,57 +150,50 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
   AtPartials part = at_carve(ws_raw, tokens, plan.segs_max);
 
   // ---------------- gather issue: tile `issued` goes to stage issued % 3 ------------------------
-  // Warp 0 issues every tile: lane l owns rows l and l + 32.
-  if (tid == 0) {
-    for (int i = 0; i < kMmStages; ++i) ptx::mbar_init(smem_u32(&sh.full[i]), 1);
-    ptx::fence_barrier_init();
-  }
-  __syncthreads();
   long ti = w0 / tpt;                 // (token, tile-in-token) of the next tile to issue
   int ji = (int)(w0 - ti * tpt);
-  int issued = 0, nv0 = -1, nv1 = -1; // the lane's two row indices of that tile, requested a tile ahead
+  int issued = 0, nv0 = -1, nv1 = -1; // its 64 indices, two per lane, requested one tile ahead
   auto load_indices = [&](long tt, int jj, int& a, int& b) {
     const int k0 = jj * kAtTile + lane, k1 = k0 + 32;
     a = k0 < topk ? __ldg(indices + (size_t)tt * index_stride + k0) : -1;
     b = k1 < topk ? __ldg(indices + (size_t)tt * index_stride + k1) : -1;
   };
-  if (w == 0) load_indices(ti, ji, nv0, nv1);
+  load_indices(ti, ji, nv0, nv1);
+  const int sub = lane >> 3, ch = lane & 7;  // row inside a 4-row group, 16-byte chunk of a 128-byte block
   auto issue_tile = [&]() {
-    if (w == 0 && issued < n) {
+    if (issued < n) {
       const int s = issued % kMmStages;
-      int v[2] = {nv0, nv1};
+      int v0 = nv0, v1 = nv1;
       if (++ji == tpt) { ji = 0; ++ti; }
       if (issued + 1 < n) load_indices(ti, ji, nv0, nv1);
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        if (v[e] >= num_slots) { raise_status(status, DSA_STATUS_BAD_SLOT); v[e] = -1; }
-        if (v[e] < 0) v[e] = -1;
+      if (v0 >= num_slots || v1 >= num_slots) {
+        raise_status(status, DSA_STATUS_BAD_SLOT);
+        if (v0 >= num_slots) v0 = -1;
+        if (v1 >= num_slots) v1 = -1;
       }
-      const int n_valid = __popc(__ballot_sync(0xffffffffu, v[0] >= 0)) +
-                          __popc(__ballot_sync(0xffffffffu, v[1] >= 0));
-      const uint32_t bar = smem_u32(&sh.full[s]);
-      if (lane == 0) {
-        sh.live[s] = n_valid > 0;
-        ptx::mbar_expect_tx(bar, n_valid * kMmRowBytes);   // the stage's single arrival
-      }
-      __syncwarp();
+      if (v0 < 0) v0 = -1;
+      if (v1 < 0) v1 = -1;
+      const bool live = __any_sync(0xffffffffu, v0 >= 0 || v1 >= 0);
+      const uint32_t dst0 = kv_addr + s * kMmStageBytes;
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int r = lane + 32 * e;
-        const uint32_t dst = kv_addr + s * kMmStageBytes + r * kMmPitch;
-        if (v[e] >= 0) {
-          ptx::bulk_load_1d(dst, ckv + (size_t)v[e] * kCkv, kCkv * 2, bar);
-          ptx::bulk_load_1d(dst + kCkv * 2, kpe + (size_t)v[e] * kKpe, kKpe * 2, bar);
-        } else if (n_valid > 0) {
-          // masked row of a tile that will be computed: its V part must read as zero
-          const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-          unsigned char* row = dyn_raw + pad + s * kMmStageBytes + r * kMmPitch;
-#pragma unroll 8
-          for (int c = 0; c < kMmRowBytes / 16; ++c) *reinterpret_cast<uint4*>(row + c * 16) = z;
+      for (int gi = 0; gi < 2; ++gi) {       // this warp copies row groups w and w + 8
+        const int r = 4 * (w + 8 * gi) + sub;
+        const int a = __shfl_sync(0xffffffffu, v0, r & 31), b = __shfl_sync(0xffffffffu, v1, r & 31);
+        const int sl = r < 32 ? a : b;
+        if (live) {
+          const uint32_t nbytes = sl >= 0 ? 16u : 0u;
+          const __nv_bfloat16* src_c = ckv + ((size_t)(sl >= 0 ? sl : 0) * kCkv + ch * 8);
+          const __nv_bfloat16* src_p = kpe + ((size_t)(sl >= 0 ? sl : 0) * kKpe + ch * 8);
+          const uint32_t dst = dst0 + r * 128 + ((ch ^ (r & 7)) << 4);
+#pragma unroll
+          for (int kb = 0; kb < 8; ++kb) ptx::cp_async16(dst + kb * kMmBlockBytes, src_c + kb * 64, nbytes);
+          ptx::cp_async16(dst + 8 * kMmBlockBytes, src_p, nbytes);
         }
-        sh.idx[s][r] = v[e];
+        if (ch == 0) sh.idx[s][r] = sl;
       }
+      if (tid == 0) sh.live[s] = live ? 1 : 0;
     }
+    cp_async_commit();  // always: keeps "all but the newest group" == "tile i has landed"
     ++issued;
   };
   issue_tile();
@@ -240,28 +229,24 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
       l0 = l1 = 0.f;
       cur_t = t;
     }
-    const int s = i % kMmStages;
-    // tile i has landed (bounded wait); the barrier also means everyone is done with tile i-1
-    const bool landed = ptx::mbar_wait(smem_u32(&sh.full[s]), (uint32_t)((i / kMmStages) & 1));
-    if (__syncthreads_or(!landed)) {
-      if (tid == 0) raise_status(status, DSA_STATUS_WAIT_TIMEOUT);
-      for (int z = 0; z < 64; ++z) __nanosleep(20000);  // let copies already issued land before exit
-      break;
-    }
+    cp_async_wait_group<1>();   // tile i has landed (only the newest group, tile i+1, may be pending)
+    __syncthreads();            // ... for every thread; and everyone is done with tile i-1
     issue_tile();               // tile i+2 -> the stage tile i-1 used
+    const int s = i % kMmStages;
     if (sh.live[s]) {
       const uint32_t sa = kv_addr + s * kMmStageBytes;
       // ---- S = Q . K^T for rows 8w .. 8w+7 -----------------------------------------------------
       float sacc[4] = {0.f, 0.f, 0.f, 0.f};
       {
         const int row_l = 8 * w + (lane & 7);
-        const uint32_t brow = sa + row_l * kMmPitch + ((lane >> 3) << 4);
+        const uint32_t brow = sa + row_l * 128;
+        const int rx = row_l & 7, quad = lane >> 3;
 #pragma unroll
         for (int kb = 0; kb < 9; ++kb) {
 #pragma unroll
           for (int kk = 0; kk < 2; ++kk) {
             uint32_t r0, r1, r2, r3;
-            ldsm_x4(brow + (kb * 8 + kk * 4) * 16, r0, r1, r2, r3);
+            ldsm_x4(brow + kb * kMmBlockBytes + (((kk * 4 + quad) ^ rx) << 4), r0, r1, r2, r3);
             hmma_16816(sacc, qa[kb * 4 + 2 * kk], r0, r1);
             hmma_16816(sacc, qa[kb * 4 + 2 * kk + 1], r2, r3);
           }
@@ -305,16 +290,17 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
       {
         const int hrow = (lane & 7) + ((lane >> 3) & 1) * 8, half = lane >> 4;
         const uint32_t pa = p_addr + hrow * 128;
-        const uint32_t vbase = sa + w * 128 + half * 16;
+        const uint32_t vbase = sa + w * kMmBlockBytes;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
           uint32_t a[4];
           ldsm_x4(pa + (((ks * 2 + half) ^ (hrow & 7)) << 4), a[0], a[1], a[2], a[3]);
-          const uint32_t va_addr = vbase + (ks * 16 + hrow) * kMmPitch;
+          const int vrow = ks * 16 + hrow;
+          const uint32_t va_addr = vbase + vrow * 128;
 #pragma unroll
           for (int np = 0; np < 4; ++np) {
             uint32_t r0, r1, r2, r3;
-            ldsm_x4_trans(va_addr + np * 32, r0, r1, r2, r3);
+            ldsm_x4_trans(va_addr + (((np * 2 + half) ^ (vrow & 7)) << 4), r0, r1, r2, r3);
             hmma_16816(o[2 * np], a, r0, r1);
             hmma_16816(o[2 * np + 1], a, r2, r3);
           }
@@ -381,6 +367,7 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
       }
     }
   }
+  cp_async_wait_group<0>();
 }
 
 cudaError_t launch_sparse_attn_mma(const void* q_nope, const void* q_pe, const void* ckv,
