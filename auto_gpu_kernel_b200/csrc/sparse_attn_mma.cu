@@ -208,29 +208,33 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
 
   for (int i = 0; i < n; ++i) {
     if (++j == tpt) { j = 0; ++t; }
-    if (t != cur_t) {
-      const __nv_bfloat16* qn0 = q_nope + (size_t)(t * kHeads + g) * kCkv;
-      const __nv_bfloat16* qn1 = qn0 + 8 * kCkv;
-      const __nv_bfloat16* qp0 = q_pe + (size_t)(t * kHeads + g) * kKpe;
-      const __nv_bfloat16* qp1 = qp0 + 8 * kKpe;
-#pragma unroll
-      for (int ks = 0; ks < 36; ++ks) {
-        const int c = (ks < 32 ? ks * 16 : (ks - 32) * 16) + 2 * t4;
-        const __nv_bfloat16* r0 = ks < 32 ? qn0 : qp0;
-        const __nv_bfloat16* r1 = ks < 32 ? qn1 : qp1;
-        qa[ks][0] = __ldg(reinterpret_cast<const uint32_t*>(r0 + c));
-        qa[ks][1] = __ldg(reinterpret_cast<const uint32_t*>(r1 + c));
-        qa[ks][2] = __ldg(reinterpret_cast<const uint32_t*>(r0 + c + 8));
-        qa[ks][3] = __ldg(reinterpret_cast<const uint32_t*>(r1 + c + 8));
+    const bool new_token = t != cur_t;
+    cp_async_wait_group<1>();   // tile i has landed (only the newest group, tile i+1, may be pending)
+    __syncthreads();            // ... for every thread; and everyone is done with tile i-1
+    if (new_token) {
+      // q of the new token: staged once, coalesced, in the stage that tile i-1 has just left (it is
+      // handed to tile i+2 right after), then read as the 36 A fragments by every warp.  Rows of
+      // 1152 B at a pitch of 1168 B keep the ldmatrix reads conflict-free.
+      const uint32_t qs = kv_addr + ((i + 2) % kMmStages) * kMmStageBytes;
+      for (int c = tid; c < kHeads * 72; c += kMmThreads) {
+        const int h = c / 72, jj = c - h * 72;
+        const __nv_bfloat16* src = jj < 64 ? q_nope + ((size_t)(t * kHeads + h) * kCkv + jj * 8)
+                                           : q_pe + ((size_t)(t * kHeads + h) * kKpe + (jj - 64) * 8);
+        ptx::cp_async16(qs + h * 1168 + jj * 16, src, 16);
       }
+      cp_async_commit();
+      cp_async_wait_group<0>();
+      __syncthreads();
+      const uint32_t qrow = qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * 1168 + (lane >> 4) * 16;
+#pragma unroll
+      for (int ks = 0; ks < 36; ++ks) ldsm_x4(qrow + ks * 32, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
 #pragma unroll
       for (int nn = 0; nn < 8; ++nn) o[nn][0] = o[nn][1] = o[nn][2] = o[nn][3] = 0.f;
       m0 = m1 = -INFINITY;
       l0 = l1 = 0.f;
       cur_t = t;
+      __syncthreads();          // the staging area may now be overwritten by tile i+2
     }
-    cp_async_wait_group<1>();   // tile i has landed (only the newest group, tile i+1, may be pending)
-    __syncthreads();            // ... for every thread; and everyone is done with tile i-1
     issue_tile();               // tile i+2 -> the stage tile i-1 used
     const int s = i % kMmStages;
     if (sh.live[s]) {
