@@ -12,15 +12,12 @@
 // instructions = 1.1 k cycles, and the kernel is bound by the gather as it should be.
 //
 // Structure (one CTA of 8 warps per SM, no warp specialisation, no mbarrier, nothing that spins):
-//   * three 64-row stages in shared memory.  A row is stored as it is in HBM (1024 B ckv then
-//     128 B kpe) at a pitch of 1168 B (73 x 16 B, odd), which makes both ldmatrix patterns below
-//     conflict-free without a swizzle.  The gather is split over two engines, two tiles ahead:
-//     the ckv part of rows 0-31 by one 1024-byte cp.async.bulk each (completion on an mbarrier
-//     per stage), everything else by 16-byte cp.async from all warps.  Measured alone, the 16-byte
-//     copies sustain ~27 B/clk/SM through the load/store unit, which the ldmatrix traffic (153 KB
-//     per tile) shares, and the bulk engine costs ~90 cycles per request whatever its size
-//     (all-bulk: 92.7 us; all-cp.async: 43 us for the headline shape), so neither alone reaches
-//     HBM speed; masked rows (-1) are zero-filled;
+//   * three 64-row stages in shared memory, filled by cp.async 16-byte copies issued by all warps
+//     two tiles ahead; a tile is nine [64 rows x 128 B] blocks (8 ckv column blocks + kpe) with the
+//     16-byte chunks of a row XOR-swizzled by (row & 7), so both ldmatrix patterns below are
+//     conflict-free; masked rows (-1) are zero-filled.  (Fetching rows with cp.async.bulk, 1024 B +
+//     128 B per row into linear padded rows, was measured at 92.7 us for the headline shape against
+//     50.5 us for these 16-byte copies: the bulk engine costs ~70 cycles per request.);
 //   * S[16 heads, 64 rows] = Q.K^T: warp w owns rows 8w..8w+7; q lives in registers as the 36
 //     A fragments of the token (loaded once per token), K fragments come from ldmatrix.x4;
 //   * online softmax in base 2 with a lazily refreshed running max (refreshed, and O rescaled in
@@ -40,9 +37,8 @@
 namespace dsa {
 
 constexpr int kMmStages = 3;
-constexpr int kMmPitch = 1168;                       // bytes between rows of a stage: 1152 data + 16
-constexpr int kMmStageBytes = kAtTile * kMmPitch;   // 74752
-constexpr int kMmBulkRows = 32;                     // rows 0..31 of a tile: ckv part by bulk copy
+constexpr int kMmBlockBytes = kAtTile * 128;        // 8192
+constexpr int kMmStageBytes = 9 * kMmBlockBytes;    // 73728
 constexpr int kMmThreads = 256;
 constexpr int kMmPBytes = kHeads * 128;             // P^T [16 heads][64 rows] bf16
 constexpr float kMmLog2e = 1.4426950408889634f;
@@ -51,7 +47,6 @@ constexpr float kMmRescaleGap = 8.f;
 struct MmShared {
   int idx[kMmStages][kAtTile];
   int live[kMmStages];
-  uint64_t full[kMmStages];   // completion of the bulk copies of a stage
   float red[8][kHeads];
   float merge_f[32][kHeads];
   float merge_inv[kHeads];
@@ -164,11 +159,6 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
     b = k1 < topk ? __ldg(indices + (size_t)tt * index_stride + k1) : -1;
   };
   load_indices(ti, ji, nv0, nv1);
-  if (tid == 0) {
-    for (int i = 0; i < kMmStages; ++i) ptx::mbar_init(smem_u32(&sh.full[i]), 1);
-    ptx::fence_barrier_init();
-  }
-  __syncthreads();
   const int sub = lane >> 3, ch = lane & 7;  // row inside a 4-row group, 16-byte chunk of a 128-byte block
   auto issue_tile = [&]() {
     if (issued < n) {
@@ -185,12 +175,6 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
       if (v1 < 0) v1 = -1;
       const bool live = __any_sync(0xffffffffu, v0 >= 0 || v1 >= 0);
       const uint32_t dst0 = kv_addr + s * kMmStageBytes;
-      const uint32_t bar = smem_u32(&sh.full[s]);
-      const int n_bulk = __popc(__ballot_sync(0xffffffffu, v0 >= 0));  // valid rows among rows 0..31
-      if (tid == 0) {
-        sh.live[s] = live ? 1 : 0;
-        ptx::mbar_expect_tx(bar, live ? n_bulk * (kCkv * 2) : 0);  // the stage's single arrival
-      }
 #pragma unroll
       for (int gi = 0; gi < 2; ++gi) {       // this warp copies row groups w and w + 8
         const int r = 4 * (w + 8 * gi) + sub;
@@ -200,27 +184,14 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
           const uint32_t nbytes = sl >= 0 ? 16u : 0u;
           const __nv_bfloat16* src_c = ckv + ((size_t)(sl >= 0 ? sl : 0) * kCkv + ch * 8);
           const __nv_bfloat16* src_p = kpe + ((size_t)(sl >= 0 ? sl : 0) * kKpe + ch * 8);
-          const uint32_t dst = dst0 + r * kMmPitch + ch * 16;
-          if (gi == 0) {
-            // rows 0..31: the 1024-byte ckv part goes through the bulk engine (one lane per row)
-            if (ch == 0) {
-              if (sl >= 0) {
-                ptx::bulk_load_1d(dst, ckv + (size_t)sl * kCkv, kCkv * 2, bar);
-              } else {
-                const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-                unsigned char* row = dyn_raw + pad + s * kMmStageBytes + r * kMmPitch;
-#pragma unroll 8
-                for (int c = 0; c < kCkv * 2 / 16; ++c) *reinterpret_cast<uint4*>(row + c * 16) = z;
-              }
-            }
-          } else {
+          const uint32_t dst = dst0 + r * 128 + ((ch ^ (r & 7)) << 4);
 #pragma unroll
-            for (int kb = 0; kb < 8; ++kb) ptx::cp_async16(dst + kb * 128, src_c + kb * 64, nbytes);
-          }
-          ptx::cp_async16(dst + kCkv * 2, src_p, nbytes);
+          for (int kb = 0; kb < 8; ++kb) ptx::cp_async16(dst + kb * kMmBlockBytes, src_c + kb * 64, nbytes);
+          ptx::cp_async16(dst + 8 * kMmBlockBytes, src_p, nbytes);
         }
         if (ch == 0) sh.idx[s][r] = sl;
       }
+      if (tid == 0) sh.live[s] = live ? 1 : 0;
     }
     cp_async_commit();  // always: keeps "all but the newest group" == "tile i has landed"
     ++issued;
@@ -238,14 +209,8 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
   for (int i = 0; i < n; ++i) {
     if (++j == tpt) { j = 0; ++t; }
     const bool new_token = t != cur_t;
-    cp_async_wait_group<1>();   // this thread's 16-byte copies of tile i have landed (tile i+1 may be pending)
-    const bool landed = ptx::mbar_wait(smem_u32(&sh.full[i % kMmStages]), (uint32_t)((i / kMmStages) & 1));
-    // barrier: tile i is complete for every thread, and everyone is done with tile i-1
-    if (__syncthreads_or(!landed)) {
-      if (tid == 0) raise_status(status, DSA_STATUS_WAIT_TIMEOUT);
-      for (int z = 0; z < 64; ++z) __nanosleep(20000);  // let bulk copies already issued land
-      break;
-    }
+    cp_async_wait_group<1>();   // tile i has landed (only the newest group, tile i+1, may be pending)
+    __syncthreads();            // ... for every thread; and everyone is done with tile i-1
     if (new_token) {
       // q of the new token: staged once, coalesced, in the stage that tile i-1 has just left (it is
       // handed to tile i+2 right after), then read as the 36 A fragments by every warp.  Rows of
@@ -255,12 +220,12 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
         const int h = c / 72, jj = c - h * 72;
         const __nv_bfloat16* src = jj < 64 ? q_nope + ((size_t)(t * kHeads + h) * kCkv + jj * 8)
                                            : q_pe + ((size_t)(t * kHeads + h) * kKpe + (jj - 64) * 8);
-        ptx::cp_async16(qs + h * kMmPitch + jj * 16, src, 16);
+        ptx::cp_async16(qs + h * 1168 + jj * 16, src, 16);
       }
       cp_async_commit();
       cp_async_wait_group<0>();
       __syncthreads();
-      const uint32_t qrow = qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * kMmPitch + (lane >> 4) * 16;
+      const uint32_t qrow = qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * 1168 + (lane >> 4) * 16;
 #pragma unroll
       for (int ks = 0; ks < 36; ++ks) ldsm_x4(qrow + ks * 32, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
 #pragma unroll
@@ -277,13 +242,15 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
       // ---- S = Q . K^T for rows 8w .. 8w+7 -----------------------------------------------------
       float sacc[4] = {0.f, 0.f, 0.f, 0.f};
       {
-        const uint32_t brow = sa + (8 * w + (lane & 7)) * kMmPitch + ((lane >> 3) << 4);
+        const int row_l = 8 * w + (lane & 7);
+        const uint32_t brow = sa + row_l * 128;
+        const int rx = row_l & 7, quad = lane >> 3;
 #pragma unroll
         for (int kb = 0; kb < 9; ++kb) {
 #pragma unroll
           for (int kk = 0; kk < 2; ++kk) {
             uint32_t r0, r1, r2, r3;
-            ldsm_x4(brow + (kb * 8 + kk * 4) * 16, r0, r1, r2, r3);
+            ldsm_x4(brow + kb * kMmBlockBytes + (((kk * 4 + quad) ^ rx) << 4), r0, r1, r2, r3);
             hmma_16816(sacc, qa[kb * 4 + 2 * kk], r0, r1);
             hmma_16816(sacc, qa[kb * 4 + 2 * kk + 1], r2, r3);
           }
@@ -327,16 +294,17 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
       {
         const int hrow = (lane & 7) + ((lane >> 3) & 1) * 8, half = lane >> 4;
         const uint32_t pa = p_addr + hrow * 128;
-        const uint32_t vbase = sa + w * 128 + half * 16;
+        const uint32_t vbase = sa + w * kMmBlockBytes;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
           uint32_t a[4];
           ldsm_x4(pa + (((ks * 2 + half) ^ (hrow & 7)) << 4), a[0], a[1], a[2], a[3]);
-          const uint32_t va_addr = vbase + (ks * 16 + hrow) * kMmPitch;
+          const int vrow = ks * 16 + hrow;
+          const uint32_t va_addr = vbase + vrow * 128;
 #pragma unroll
           for (int np = 0; np < 4; ++np) {
             uint32_t r0, r1, r2, r3;
-            ldsm_x4_trans(va_addr + np * 32, r0, r1, r2, r3);
+            ldsm_x4_trans(va_addr + (((np * 2 + half) ^ (vrow & 7)) << 4), r0, r1, r2, r3);
             hmma_16816(o[2 * np], a, r0, r1);
             hmma_16816(o[2 * np + 1], a, r2, r3);
           }
