@@ -240,7 +240,10 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
     if (sh.live[s]) {
       const uint32_t sa = kv_addr + s * kMmStageBytes;
       // ---- S = Q . K^T for rows 8w .. 8w+7 -----------------------------------------------------
-      float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+      // four accumulator chains (one per k-step of a column block): a single chain of 36
+      // dependent mma.sync would be latency-bound
+      float sacc[4] = {0.f, 0.f, 0.f, 0.f}, sb[4] = {0.f, 0.f, 0.f, 0.f};
+      float sc[4] = {0.f, 0.f, 0.f, 0.f}, sd[4] = {0.f, 0.f, 0.f, 0.f};
       {
         const int row_l = 8 * w + (lane & 7);
         const uint32_t brow = sa + row_l * 128;
@@ -251,18 +254,34 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
           for (int kk = 0; kk < 2; ++kk) {
             uint32_t r0, r1, r2, r3;
             ldsm_x4(brow + kb * kMmBlockBytes + (((kk * 4 + quad) ^ rx) << 4), r0, r1, r2, r3);
-            hmma_16816(sacc, qa[kb * 4 + 2 * kk], r0, r1);
-            hmma_16816(sacc, qa[kb * 4 + 2 * kk + 1], r2, r3);
+            if (kk == 0) {
+              hmma_16816(sacc, qa[kb * 4], r0, r1);
+              hmma_16816(sb, qa[kb * 4 + 1], r2, r3);
+            } else {
+              hmma_16816(sc, qa[kb * 4 + 2], r0, r1);
+              hmma_16816(sd, qa[kb * 4 + 3], r2, r3);
+            }
           }
         }
       }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sacc[e] = (sacc[e] + sb[e]) + (sc[e] + sd[e]);
       const int ra = 8 * w + 2 * t4;
       const bool va = sh.idx[s][ra] >= 0, vb = sh.idx[s][ra + 1] >= 0;
       const float x0 = va ? sacc[0] * scale_log2 : -INFINITY, x1 = vb ? sacc[1] * scale_log2 : -INFINITY;
       const float x2 = va ? sacc[2] * scale_log2 : -INFINITY, x3 = vb ? sacc[3] * scale_log2 : -INFINITY;
       const bool need = fmaxf(x0, x1) > m0 + kMmRescaleGap || fmaxf(x2, x3) > m1 + kMmRescaleGap;
+      // P^T[head][row]: rows 8w..8w+7 are 16-byte chunk w of the head's 128-byte line
+      uint32_t* pa0 = reinterpret_cast<uint32_t*>(p_ptr + g * 128 + ((w ^ (g & 7)) << 4) + t4 * 4);
+      uint32_t* pa1 = reinterpret_cast<uint32_t*>(p_ptr + (g + 8) * 128 + ((w ^ (g & 7)) << 4) + t4 * 4);
+      float u0 = m0 == -INFINITY ? 0.f : m0, u1 = m1 == -INFINITY ? 0.f : m1;
+      float p0 = exp2f(x0 - u0), p1 = exp2f(x1 - u0), p2 = exp2f(x2 - u1), p3 = exp2f(x3 - u1);
+      // optimistic: publish P with the running max as it is; the same barrier that makes P visible
+      // tells whether some logit exceeded the max by more than 2^8 (rare)
+      *pa0 = pack_bf162(p0, p1);
+      *pa1 = pack_bf162(p2, p3);
       if (__syncthreads_or(need)) {
-        // refresh the running max of every head over the tile, rescale the accumulators
+        // refresh the running max of every head over the tile, rescale the accumulators, redo P
         float v0 = fmaxf(x0, x1), v1 = fmaxf(x2, x3);
         v0 = fmaxf(v0, __shfl_xor_sync(0xffffffffu, v0, 1));
         v0 = fmaxf(v0, __shfl_xor_sync(0xffffffffu, v0, 2));
@@ -279,17 +298,14 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
         for (int nn = 0; nn < 8; ++nn) { o[nn][0] *= c0; o[nn][1] *= c0; o[nn][2] *= c1; o[nn][3] *= c1; }
         l0 *= c0; l1 *= c1;
         m0 = n0; m1 = n1;
+        u0 = m0 == -INFINITY ? 0.f : m0; u1 = m1 == -INFINITY ? 0.f : m1;
+        p0 = exp2f(x0 - u0); p1 = exp2f(x1 - u0); p2 = exp2f(x2 - u1); p3 = exp2f(x3 - u1);
+        *pa0 = pack_bf162(p0, p1);
+        *pa1 = pack_bf162(p2, p3);
+        __syncthreads();
       }
-      {
-        const float u0 = m0 == -INFINITY ? 0.f : m0, u1 = m1 == -INFINITY ? 0.f : m1;
-        const float p0 = exp2f(x0 - u0), p1 = exp2f(x1 - u0), p2 = exp2f(x2 - u1), p3 = exp2f(x3 - u1);
-        l0 += p0 + p1;
-        l1 += p2 + p3;
-        // P^T[head][row]: rows 8w..8w+7 are 16-byte chunk w of the head's 128-byte line
-        *reinterpret_cast<uint32_t*>(p_ptr + g * 128 + ((w ^ (g & 7)) << 4) + t4 * 4) = pack_bf162(p0, p1);
-        *reinterpret_cast<uint32_t*>(p_ptr + (g + 8) * 128 + ((w ^ (g & 7)) << 4) + t4 * 4) = pack_bf162(p2, p3);
-      }
-      __syncthreads();
+      l0 += p0 + p1;
+      l1 += p2 + p3;
       // ---- O += P . V for columns 64w .. 64w+63 (column block w of the tile) ---------------------
       {
         const int hrow = (lane & 7) + ((lane >> 3) & 1) * 8, half = lane >> 4;
