@@ -196,6 +196,18 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
     cp_async_commit();  // always: keeps "all but the newest group" == "tile i has landed"
     ++issued;
   };
+  // q of the first token is requested before the first two tiles, into the third stage, so that
+  // its latency overlaps theirs
+  auto stage_q = [&](long tt, uint32_t qs) {
+    for (int c = tid; c < kHeads * 72; c += kMmThreads) {
+      const int h = c / 72, jj = c - h * 72;
+      const __nv_bfloat16* src = jj < 64 ? q_nope + ((size_t)(tt * kHeads + h) * kCkv + jj * 8)
+                                         : q_pe + ((size_t)(tt * kHeads + h) * kKpe + (jj - 64) * 8);
+      ptx::cp_async16(qs + h * 1168 + jj * 16, src, 16);
+    }
+    cp_async_commit();
+  };
+  stage_q(w0 / tpt, kv_addr + 2 * kMmStageBytes);
   issue_tile();
   issue_tile();
 
@@ -216,15 +228,11 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
       // handed to tile i+2 right after), then read as the 36 A fragments by every warp.  Rows of
       // 1152 B at a pitch of 1168 B keep the ldmatrix reads conflict-free.
       const uint32_t qs = kv_addr + ((i + 2) % kMmStages) * kMmStageBytes;
-      for (int c = tid; c < kHeads * 72; c += kMmThreads) {
-        const int h = c / 72, jj = c - h * 72;
-        const __nv_bfloat16* src = jj < 64 ? q_nope + ((size_t)(t * kHeads + h) * kCkv + jj * 8)
-                                           : q_pe + ((size_t)(t * kHeads + h) * kKpe + (jj - 64) * 8);
-        ptx::cp_async16(qs + h * 1168 + jj * 16, src, 16);
+      if (i > 0) {   // (the first token's q was requested before the loop and has landed with tile 0)
+        stage_q(t, qs);
+        cp_async_wait_group<0>();
+        __syncthreads();
       }
-      cp_async_commit();
-      cp_async_wait_group<0>();
-      __syncthreads();
       const uint32_t qrow = qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * 1168 + (lane >> 4) * 16;
 #pragma unroll
       for (int ks = 0; ks < 36; ++ks) ldsm_x4(qrow + ks * 32, qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3]);
