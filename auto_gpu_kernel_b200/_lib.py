@@ -25,6 +25,8 @@ SIGNATURES = {
     "dsa_indexer_workspace_bytes": (_c_size, [_c_int, _c_int]),
     "dsa_indexer_topk": (_c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr, _c_i64, _c_int,
                                   _c_int, _c_int, _ptr, _c_size, _ptr, _ptr]),
+    "dsa_indexer_topk_noalloc": (_c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr, _c_i64, _c_int,
+                                          _c_int, _c_int, _ptr, _ptr]),
     "dsa_indexer_scores": (_c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr, _c_i64, _c_int,
                                     _c_int, _c_int, _c_int, _ptr, _ptr]),
     "dsa_topk_select": (_c_int, [_ptr, _c_i64, _ptr, _ptr, _c_i64, _ptr, _c_i64, _c_int, _c_int,

@@ -46,6 +46,8 @@ const char* dsa_b200_error_string(int code) {
     case DSA_ERR_WORKSPACE_TOO_SMALL: return "dsa_b200: workspace too small";
     case DSA_ERR_MISALIGNED: return "dsa_b200: pointer or stride not 16-byte aligned";
     case DSA_ERR_UNSUPPORTED: return "dsa_b200: variant not available";
+    case DSA_ERR_SCRATCH_TOO_SMALL:
+      return "dsa_b200: batch x context exceeds the built-in scratch of dsa_indexer_topk_noalloc";
     default: break;
   }
   if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));

@@ -40,7 +40,8 @@ enum {
   DSA_ERR_BAD_SHAPE = -2,
   DSA_ERR_WORKSPACE_TOO_SMALL = -3,
   DSA_ERR_MISALIGNED = -4,
-  DSA_ERR_UNSUPPORTED = -5
+  DSA_ERR_UNSUPPORTED = -5,
+  DSA_ERR_SCRATCH_TOO_SMALL = -6 /* dsa_indexer_topk_noalloc: batch x padded context > built-in scratch */
 };
 
 /* bits OR-ed into *status_dev by kernels */
@@ -78,6 +79,30 @@ int dsa_indexer_topk(const void* q_fp8, const void* k_cache, const float* weight
                      int64_t block_table_stride, int32_t* topk_out, int64_t topk_stride,
                      int batch, int num_pages, int max_pages, void* workspace,
                      size_t workspace_bytes, int32_t* status_dev, void* stream);
+
+/* The same indexer for callers that cannot allocate device memory (no counterpart in the
+ * reference: its callers always own an allocator).  Use it from places where cudaMalloc is not an
+ * option -- a frozen memory pool of a serving loop, a plugin that may only touch the tensors it was
+ * handed, a process whose allocator belongs to another runtime -- and the score workspace of
+ * dsa_indexer_topk therefore cannot be provided.  The scores go to a fixed array inside the
+ * library's device image instead (DSA_NOALLOC_MAX_SCORES fp32 values = 8 MiB, resident on every
+ * GPU that loads the library until the process exits).
+ *   - limit: batch * round_up(max_pages * 64, 128) <= DSA_NOALLOC_MAX_SCORES, e.g. 64 requests of
+ *     32768 tokens; larger calls return DSA_ERR_SCRATCH_TOO_SMALL and launch nothing;
+ *   - the call allocates nothing: no cudaMalloc/cudaFree, no allocating library routine;
+ *   - the first call on each device looks the array's device address up once
+ *     (cudaGetSymbolAddress); make that first call outside any stream capture;
+ *   - every call on a device shares the one array: two calls that overlap on the GPU (different
+ *     streams, no dependency) race on it and corrupt each other's result; calls on one stream, or
+ *     ordered by events, are fine.  The array keeps the previous call's scores; nothing relies on
+ *     its initial contents.
+ * Arguments as for dsa_indexer_topk, minus the workspace. */
+#define DSA_NOALLOC_MAX_SCORES (2u * 1024u * 1024u)
+int dsa_indexer_topk_noalloc(const void* q_fp8, const void* k_cache, const float* weights,
+                             const int32_t* seq_lens, const int32_t* block_table,
+                             int64_t block_table_stride, int32_t* topk_out, int64_t topk_stride,
+                             int batch, int num_pages, int max_pages, int32_t* status_dev,
+                             void* stream);
 
 /* Stage 1 alone: fp32 score rows, scores[b*score_stride + t] for t < seq_len[b] (the quantity
  * `final_scores` of indexer_baseline.py:80).  Entries t >= seq_len[b] are left untouched.
