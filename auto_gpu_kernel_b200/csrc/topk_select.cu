@@ -162,29 +162,15 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   };
 
   // ---- sweep B: histogram of the linear bins ---------------------------------------------------
-  // For a staged row (<= 48 elements per thread) every thread keeps the bin numbers of its own
-  // elements in registers (bin + 1 in 16 bits, two per register, 0 = no element), so the count and
-  // emit sweeps below touch neither shared memory nor the float pipeline again.
-  constexpr int kPerThread = kSelRowCap / kSelThreads;  // 48
-  uint32_t binreg[kPerThread / 2];
-  if (staged) {
-#pragma unroll
-    for (int k = 0; k < kPerThread / 2; ++k) {
-      uint32_t packed = 0;
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int i = tid + (2 * k + e) * kSelThreads;
-        if (i < len) {
-          const int bn = bin_of(row_s[i]);
-          atomicAdd(&sh.hist[bn], 1u);
-          packed |= (uint32_t)(bn + 1) << (16 * e);
-        }
-      }
-      binreg[k] = packed;
-    }
-  } else {
-    for (int i = tid; i < len; i += kSelThreads) atomicAdd(&sh.hist[bin_of(__ldg(row + i))], 1u);
+  // When the row is staged, its shared-memory copy is overwritten by the bin numbers: the later
+  // sweeps only compare bins, and the few boundary-bin elements re-read their score from L2.
+  int* bin_s = reinterpret_cast<int*>(row_s);
+  for (int i = tid; i < len; i += kSelThreads) {
+    const int bn = bin_of(value_at(i));
+    if (staged) bin_s[i] = bn;
+    atomicAdd(&sh.hist[bn], 1u);
   }
+  auto bin_at = [&](int i) -> int { return staged ? bin_s[i] : bin_of(__ldg(row + i)); };
   __syncthreads();
   find_boundary_bin(sh, kSelBins, kTopK);
   const int edge = (int)sh.digit;          // boundary bin
@@ -200,15 +186,8 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   // (and no dependent round trip) inside the per-element loops.
   const int sweeps = (len + kSelThreads - 1) / kSelThreads;
   {
-    const uint32_t e1 = (uint32_t)edge + 1u;
     uint32_t mine = 0;
-    if (staged) {
-#pragma unroll
-      for (int k = 0; k < kPerThread / 2; ++k)
-        mine += ((binreg[k] & 0xffffu) > e1 ? 1u : 0u) + ((binreg[k] >> 16) > e1 ? 1u : 0u);
-    } else {
-      for (int i = tid; i < len; i += kSelThreads) mine += bin_of(__ldg(row + i)) > edge ? 1u : 0u;
-    }
+    for (int i = tid; i < len; i += kSelThreads) mine += bin_at(i) > edge ? 1u : 0u;
     uint32_t incl = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -219,26 +198,17 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
     if (lane == 31) base = atomicAdd(&sh.cnt_gt, incl);
     base = __shfl_sync(0xffffffffu, base, 31);
     uint32_t pos = base + incl - mine;
-    auto take = [&](int i, uint32_t b1, float v) {
-      if (b1 > e1) {
+    for (int i = tid; i < len; i += kSelThreads) {
+      const int bin = bin_at(i);
+      if (bin > edge) {
         if (pos < (uint32_t)kTopK) out_row[pos] = slot_of(i);
         ++pos;
-      } else if (few && b1 == e1) {
+      } else if (few && bin == edge) {
         const uint32_t c = atomicAdd(&sh.cnt_cand, 1u);
-        if (c < (uint32_t)kSelCandCap) { sh.cand_key[c] = float_to_ordered(v); sh.cand_idx[c] = i; }
-      }
-    };
-    if (staged) {
-#pragma unroll
-      for (int k = 0; k < kPerThread / 2; ++k) {
-        const uint32_t lo16 = binreg[k] & 0xffffu, hi16 = binreg[k] >> 16;
-        if (lo16 >= e1) { const int i = tid + (2 * k) * kSelThreads; take(i, lo16, row_s[i]); }
-        if (hi16 >= e1) { const int i = tid + (2 * k + 1) * kSelThreads; take(i, hi16, row_s[i]); }
-      }
-    } else {
-      for (int i = tid; i < len; i += kSelThreads) {
-        const float v = __ldg(row + i);
-        take(i, (uint32_t)bin_of(v) + 1u, v);
+        if (c < (uint32_t)kSelCandCap) {
+          sh.cand_key[c] = float_to_ordered(__ldg(row + i));
+          sh.cand_idx[c] = i;
+        }
       }
     }
   }
@@ -266,8 +236,8 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   }
 
   // ---- fallback: radix descent over the ordered keys of the boundary bin ------------------------
-  auto key_in_edge = [&](int i, uint32_t& key) -> bool {
-    const float v = value_at(i);
+  auto key_in_edge = [&](int i, uint32_t& key) -> bool {  // the staged copy now holds bins
+    const float v = __ldg(row + i);
     key = float_to_ordered(v);
     return bin_of(v) == edge;
   };
