@@ -135,6 +135,82 @@ def block_to_cpu(block):
                                 block.ckv_cache.cpu(), block.kpe_cache.cpu(), block.sm_scale)
 
 
+# ------------------------------------------------------------------------------ head-sharded block
+def run_head_sharded(args, rank, world, dev):
+    """BASELINE's full-block layout: B = 128 requests, ctx uniform in [16K, 64K]; the indexer is
+    request-sharded, its int32 [B, 2048] index rows are all-gathered (NCCL), attention runs for all
+    tokens on every rank for that rank's 16 heads over replicated ckv/kpe caches."""
+    import torch.distributed as dist
+    from auto_gpu_kernel_b200 import dist as dsa_dist, inputs as wl, workspace
+    batch = 128
+    lens = wl.uniform_lengths(batch, 16384, 65536, seed=0)
+    block = wl.make_decode_block_inputs(lens, seed=0, device=dev)      # identical on every rank
+    idx = block.indexer
+    gen = torch.Generator(device=dev).manual_seed(100 + rank)           # this rank's 16 heads
+    q_nope = (torch.randn(batch, 16, 512, generator=gen, device=dev) * 0.1).to(torch.bfloat16)
+    q_pe = (torch.randn(batch, 16, 64, generator=gen, device=dev) * 0.1).to(torch.bfloat16)
+    mine = dsa_dist.shard_range(batch, rank, world)
+    counts = [len(dsa_dist.shard_range(batch, r, world)) for r in range(world)]
+    sel = slice(mine.start, mine.stop)
+    local_args = (idx.q_index_fp8[sel].contiguous(), idx.k_index_cache_fp8, idx.weights[sel].contiguous(),
+                  idx.seq_lens[sel].contiguous(), idx.block_table[sel].contiguous())
+    local_idx = torch.empty(len(mine), TOPK, dtype=torch.int32, device=dev)
+    out = torch.empty(batch, 16, 512, dtype=torch.bfloat16, device=dev)
+    lse = torch.empty(batch, 16, dtype=torch.float32, device=dev)
+
+    def step():
+        dsa_dist.decode_block_head_sharded(local_args, counts, q_nope, q_pe, block.ckv_cache,
+                                           block.kpe_cache, block.sm_scale, out, lse,
+                                           local_indices=local_idx)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    workspace.check_status(dev)
+    sampler = ClockSampler(dev.index)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    t_load = time.perf_counter()
+    while time.perf_counter() - t_load < 1.2:
+        for _ in range(10):
+            step()
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
+    clocks["window"] = "timed steps, then the same steps repeated for 1.2 s"
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        us = t.item() / args.steps * 1e3
+        my_tokens = sum(lens[i] for i in mine)
+        line = {"metric": "us/layer: full DSA block, 128 heads = 16/GPU, decode B=128 ctx 16-64K",
+                "value": us, "unit": "us", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "strong",
+                "vs_baseline": None, "dtype": "fp8(e4m3)+bf16, fp32 accumulate", "data": "synthetic",
+                "config": {"workload": "dsa_full_block B=128 ctx~U[16K,64K] heads=16/GPU",
+                           "indexer": f"request-sharded, {len(mine)} requests / {my_tokens} cached tokens on rank 0",
+                           "collective": "all_gather int32 [128,2048] (1 MiB)" if world > 1 else "none (1 GPU)",
+                           "attention": "head-sharded, all 128 tokens per rank, caches replicated"},
+                "impl": "b200", "gpu_launches": 3 * args.steps, "clocks": clocks}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
 # ------------------------------------------------------------------------------ main
 def main():
     ap = argparse.ArgumentParser()
@@ -142,6 +218,10 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--layout", default="requests", choices=["requests", "heads"],
+                    help="requests: every rank owns its requests, no collective (default, the headline "
+                         "metric); heads: BASELINE's full 128-head block -- indexer request-sharded, "
+                         "all-gather of the index rows, attention head-sharded")
     ap.add_argument("--batch", type=int, default=BATCH, help=argparse.SUPPRESS)
     ap.add_argument("--context", type=int, default=CONTEXT, help=argparse.SUPPRESS)
     ap.add_argument("--cpu-requests", type=int, default=16, help=argparse.SUPPRESS)
@@ -187,6 +267,9 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+
+    if args.layout == "heads":
+        return run_head_sharded(args, rank, world, dev)
 
     block = wl.make_decode_block_inputs(lens, seed=rank, device=dev)
     idx = block.indexer
