@@ -1,8 +1,11 @@
 // Top-2048 selection over one fp32 score row per request, fused with the page -> global slot
 // remap and the -1 padding (reference: torch.topk + remap, indexer_baseline.py:60, :82-90).
 //
-// One CTA (1024 threads) per request; the row is staged in shared memory when it fits (<= 49152
-// scores), otherwise every sweep streams it from L2/global.
+// One thread-block CLUSTER of 1, 2 or 4 CTAs (1024 threads each) per request: the row is cut into
+// equal segments, one per CTA, so that a small batch still uses every SM; the CTAs exchange only
+// their min/max, their 2048-bin histograms, their counts and the few boundary candidates through
+// distributed shared memory.  A segment is staged in shared memory when it fits (<= 49152 scores),
+// otherwise every sweep streams it from L2/global.
 //
 // Fast path (three sweeps): (A) min and max of the row; (B) a 2048-bin histogram over the LINEAR
 // map of [min,max] -- scores of one request are spread over hundreds of bins, so shared-memory
@@ -15,9 +18,14 @@
 // ties) an 11+11+10 bit radix descent restricted to that bin finds the exact threshold key.
 // The selected SET is deterministic; the order inside the output row is not part of the contract.
 // Nothing here waits on another CTA.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+#include "tmap.cuh"
 
 namespace dsa {
+
+namespace cg = cooperative_groups;
 
 constexpr int kSelThreads = 1024;
 constexpr int kSelRowCap = 49152;  // scores staged in dynamic shared memory (192 KB)
@@ -34,6 +42,8 @@ struct SelShared {
   uint32_t warp_sums[32];
   uint32_t red_a[32], red_b[32];
   uint32_t digit, above, ties, cnt_gt, cnt_gt2, cnt_eq, cnt_cand, kmin, kmax;
+  uint32_t tot[kSelBins];          // histogram summed over the cluster
+  uint32_t peer_min[4], peer_max[4], peer_gt[4], peer_cand[4];  // written by the peers
 };
 
 // Inclusive prefix sum over the CTA in thread order.
@@ -63,11 +73,12 @@ __device__ __forceinline__ uint32_t block_inclusive_scan(uint32_t v, uint32_t* w
 
 // Find the digit d (bins are scanned from the top) such that count(bins > d) < k <= count(bins >= d).
 // Thread t owns bins nb-1-per*t ... downwards.  Results in sh.digit / sh.above / sh.ties.
-__device__ __forceinline__ void find_boundary_bin(SelShared& sh, uint32_t nb, uint32_t k) {
+__device__ __forceinline__ void find_boundary_bin(SelShared& sh, const uint32_t* hist, uint32_t nb,
+                                                  uint32_t k) {
   const int tid = threadIdx.x;
   const int per = nb / kSelThreads;  // 2 or 1
-  uint32_t c_hi = sh.hist[nb - 1 - per * tid];
-  uint32_t c_lo = per == 2 ? sh.hist[nb - 2 - per * tid] : 0u;
+  uint32_t c_hi = hist[nb - 1 - per * tid];
+  uint32_t c_lo = per == 2 ? hist[nb - 2 - per * tid] : 0u;
   uint32_t incl = block_inclusive_scan(c_hi + c_lo, sh.warp_sums);
   uint32_t excl = incl - (c_hi + c_lo);
   if (excl < k && k <= incl) {
@@ -87,8 +98,11 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
                    int32_t* status) {
   extern __shared__ float row_s[];
   __shared__ SelShared sh;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int csize = (int)cluster.num_blocks();   // CTAs per request: 1, 2 or 4
+  const int crank = (int)cluster.block_rank();
 
-  const int b = blockIdx.x;
+  const int b = blockIdx.x / csize;
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   int len = seq_lens[b];
@@ -103,8 +117,8 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
     return (table_staged ? sh.table[i >> 6] : table[i >> 6]) * kPage + (i & 63);
   };
 
-  if (len <= kTopK) {  // every token is selected: no scores needed
-    for (int i = tid; i < kTopK; i += kSelThreads)
+  if (len <= kTopK) {  // every token is selected: no scores needed (uniform over the cluster)
+    for (int i = crank * kSelThreads + tid; i < kTopK; i += csize * kSelThreads)
       out_row[i] = i < len ? table[i >> 6] * kPage + (i & 63) : -1;
     return;
   }
@@ -112,22 +126,26 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
     for (int i = tid; i < n_pages; i += kSelThreads) sh.table[i] = table[i];
   }
 
-  const bool staged = len <= kSelRowCap;
-  auto value_at = [&](int i) -> float { return staged ? row_s[i] : __ldg(row + i); };
+  // this CTA's segment [seg_lo, seg_hi) of the row (multiples of 4 keep the 16-byte loads aligned)
+  const int seg = ((len + csize - 1) / csize + 3) & ~3;
+  const int seg_lo = min(len, crank * seg), seg_hi = min(len, seg_lo + seg);
+  const int seg_len = seg_hi - seg_lo;
+  const bool staged = seg <= kSelRowCap;
+  auto value_at = [&](int i) -> float { return staged ? row_s[i - seg_lo] : __ldg(row + i); };
 
-  // ---- sweep A: stage the row, min / max ------------------------------------------------------
+  // ---- sweep A: stage the segment, min / max ----------------------------------------------------
   {
     float mn = INFINITY, mx = kSelFloor;
     const bool vec = (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
-    const int len4 = vec ? (len & ~3) : 0;
-    for (int i = tid * 4; i < len4; i += kSelThreads * 4) {  // 16-byte loads, all in flight at once
-      const float4 q = __ldg(reinterpret_cast<const float4*>(row + i));
+    const int n4 = vec ? (seg_len & ~3) : 0;
+    for (int i = tid * 4; i < n4; i += kSelThreads * 4) {  // 16-byte loads, all in flight at once
+      const float4 q = __ldg(reinterpret_cast<const float4*>(row + seg_lo + i));
       if (staged) *reinterpret_cast<float4*>(row_s + i) = q;
       mn = fminf(fminf(mn, fmaxf(q.x, kSelFloor)), fminf(fmaxf(q.y, kSelFloor), fminf(fmaxf(q.z, kSelFloor), fmaxf(q.w, kSelFloor))));
       mx = fmaxf(fmaxf(mx, q.x), fmaxf(q.y, fmaxf(q.z, q.w)));
     }
-    for (int i = len4 + tid; i < len; i += kSelThreads) {
-      float v = __ldg(row + i);
+    for (int i = n4 + tid; i < seg_len; i += kSelThreads) {
+      float v = __ldg(row + seg_lo + i);
       if (staged) row_s[i] = v;
       v = fmaxf(v, kSelFloor);
       mn = fminf(mn, v);
@@ -150,8 +168,20 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
         mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
       }
-      if (lane == 0) { sh.kmin = __float_as_uint(mn); sh.kmax = __float_as_uint(mx); }
+      if (lane < csize) {  // publish this CTA's min / max in every CTA of the cluster
+        SelShared* peer = cluster.map_shared_rank(&sh, lane);
+        peer->peer_min[crank] = __float_as_uint(mn);
+        peer->peer_max[crank] = __float_as_uint(mx);
+      }
     }
+    cluster.sync();
+    mn = __uint_as_float(sh.peer_min[0]);
+    mx = __uint_as_float(sh.peer_max[0]);
+    for (int r = 1; r < csize; ++r) {
+      mn = fminf(mn, __uint_as_float(sh.peer_min[r]));
+      mx = fmaxf(mx, __uint_as_float(sh.peer_max[r]));
+    }
+    if (tid == 0) { sh.kmin = __float_as_uint(mn); sh.kmax = __float_as_uint(mx); }
     __syncthreads();
   }
   const float lo = __uint_as_float(sh.kmin);
@@ -161,147 +191,176 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
     return min(kSelBins - 1, __float2int_rz((fmaxf(v, kSelFloor) - lo) * inv));
   };
 
-  // ---- sweep B: histogram of the linear bins ---------------------------------------------------
-  // When the row is staged, its shared-memory copy is overwritten by the bin numbers: the later
-  // sweeps only compare bins, and the few boundary-bin elements re-read their score from L2.
-  int* bin_s = reinterpret_cast<int*>(row_s);
-  for (int i = tid; i < len; i += kSelThreads) {
-    const int bn = bin_of(value_at(i));
-    if (staged) bin_s[i] = bn;
-    atomicAdd(&sh.hist[bn], 1u);
+  // ---- sweep B: histogram of the linear bins, summed over the cluster ---------------------------
+  for (int i = seg_lo + tid; i < seg_hi; i += kSelThreads) atomicAdd(&sh.hist[bin_of(value_at(i))], 1u);
+  cluster.sync();
+  for (int k = tid; k < kSelBins; k += kSelThreads) {
+    uint32_t c = 0;
+    for (int r = 0; r < csize; ++r) c += cluster.map_shared_rank(&sh, r)->hist[k];
+    sh.tot[k] = c;
   }
-  auto bin_at = [&](int i) -> int { return staged ? bin_s[i] : bin_of(__ldg(row + i)); };
   __syncthreads();
-  find_boundary_bin(sh, kSelBins, kTopK);
+  find_boundary_bin(sh, sh.tot, kSelBins, kTopK);   // every CTA finds the same boundary
   const int edge = (int)sh.digit;          // boundary bin
   const uint32_t above = sh.above;         // elements in higher bins: all selected
-  const uint32_t in_edge = sh.ties;        // elements in the boundary bin
+  const uint32_t in_edge = sh.ties;        // elements in the boundary bin (whole row)
   const uint32_t need = kTopK - above;     // how many of them are selected (>= 1)
   const bool few = in_edge <= (uint32_t)kSelCandCap;
   __syncthreads();
 
-  // ---- sweep C: emit everything above the boundary bin, collect the boundary bin ---------------
-  // Each thread first counts its own elements above the boundary, a warp scan plus ONE shared
-  // atomic per warp hands out contiguous output slots, then the elements are written: no atomic
-  // (and no dependent round trip) inside the per-element loops.
-  const int sweeps = (len + kSelThreads - 1) / kSelThreads;
-  {
-    uint32_t mine = 0;
-    for (int i = tid; i < len; i += kSelThreads) mine += bin_at(i) > edge ? 1u : 0u;
-    uint32_t incl = mine;
+  // ---- sweep C: count, agree on output offsets, emit; collect the boundary bin ------------------
+  uint32_t mine = 0;
+  for (int i = seg_lo + tid; i < seg_hi; i += kSelThreads) mine += bin_of(value_at(i)) > edge ? 1u : 0u;
+  uint32_t incl = mine;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const uint32_t n = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += n;
-    }
-    uint32_t base = 0;
-    if (lane == 31) base = atomicAdd(&sh.cnt_gt, incl);
-    base = __shfl_sync(0xffffffffu, base, 31);
-    uint32_t pos = base + incl - mine;
-    for (int i = tid; i < len; i += kSelThreads) {
-      const int bin = bin_at(i);
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t n = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += n;
+  }
+  uint32_t wbase = 0;
+  if (lane == 31) wbase = atomicAdd(&sh.cnt_gt, incl);
+  wbase = __shfl_sync(0xffffffffu, wbase, 31);
+  __syncthreads();
+  if (tid < csize) cluster.map_shared_rank(&sh, tid)->peer_gt[crank] = sh.cnt_gt;
+  cluster.sync();
+  uint32_t cta_base = 0;
+  for (int r = 0; r < crank; ++r) cta_base += sh.peer_gt[r];
+  {
+    uint32_t pos = cta_base + wbase + incl - mine;
+    for (int i = seg_lo + tid; i < seg_hi; i += kSelThreads) {
+      const float v = value_at(i);
+      const int bin = bin_of(v);
       if (bin > edge) {
         if (pos < (uint32_t)kTopK) out_row[pos] = slot_of(i);
         ++pos;
       } else if (few && bin == edge) {
         const uint32_t c = atomicAdd(&sh.cnt_cand, 1u);
-        if (c < (uint32_t)kSelCandCap) {
-          sh.cand_key[c] = float_to_ordered(__ldg(row + i));
-          sh.cand_idx[c] = i;
-        }
+        if (c < (uint32_t)kSelCandCap) { sh.cand_key[c] = float_to_ordered(v); sh.cand_idx[c] = i; }
       }
     }
   }
   __syncthreads();
+  if (tid == 0) cluster.map_shared_rank(&sh, 0)->peer_cand[crank] = sh.cnt_cand;
+  cluster.sync();
 
   if (few) {
-    // ---- exact ranking of the candidates: higher key first, lower position first on ties -------
-    const uint32_t n = min(sh.cnt_cand, (uint32_t)kSelCandCap);
-    if (tid < (int)n) {
-      const uint32_t ka = sh.cand_key[tid];
-      const int ia = sh.cand_idx[tid];
-      uint32_t rank = 0;
-      if (n != need) {
-        for (uint32_t j = 0; j < n; ++j) {
-          const uint32_t kb = sh.cand_key[j];
-          rank += (kb > ka) || (kb == ka && sh.cand_idx[j] < ia);
+    // ---- exact ranking of the candidates by the first CTA: higher key first, lower position
+    //      first on ties ------------------------------------------------------------------------
+    if (crank == 0) {
+      uint32_t n = min(sh.peer_cand[0], (uint32_t)kSelCandCap), gt_total = sh.peer_gt[0];
+      for (int r = 1; r < csize; ++r) {
+        const uint32_t nr = min(sh.peer_cand[r], (uint32_t)kSelCandCap - n);
+        const SelShared* peer = cluster.map_shared_rank(&sh, r);
+        for (uint32_t j = tid; j < nr; j += kSelThreads) {
+          sh.cand_key[n + j] = peer->cand_key[j];
+          sh.cand_idx[n + j] = peer->cand_idx[j];
         }
-      } else {
-        rank = tid;
+        n += nr;
+        gt_total += sh.peer_gt[r];
       }
-      if (rank < need) out_row[above + rank] = slot_of(ia);
+      __syncthreads();
+      if (tid < (int)n) {
+        const uint32_t ka = sh.cand_key[tid];
+        const int ia = sh.cand_idx[tid];
+        uint32_t rank = 0;
+        if (n != need) {
+          for (uint32_t j = 0; j < n; ++j) {
+            const uint32_t kb = sh.cand_key[j];
+            rank += (kb > ka) || (kb == ka && sh.cand_idx[j] < ia);
+          }
+        } else {
+          rank = tid;
+        }
+        if (rank < need) out_row[above + rank] = slot_of(ia);
+      }
+      if (tid == 0 && (gt_total != above || n != in_edge)) raise_status(status, DSA_STATUS_TOPK_COUNT);
     }
-    if (tid == 0 && (sh.cnt_gt != above || n != in_edge)) raise_status(status, DSA_STATUS_TOPK_COUNT);
+    cluster.sync();  // the peers' shared memory stays alive until the first CTA has read it
     return;
   }
 
-  // ---- fallback: radix descent over the ordered keys of the boundary bin ------------------------
-  auto key_in_edge = [&](int i, uint32_t& key) -> bool {  // the staged copy now holds bins
-    const float v = __ldg(row + i);
-    key = float_to_ordered(v);
-    return bin_of(v) == edge;
-  };
-  uint32_t prefix = 0, mask = 0, k_rem = need;
+  // ---- fallback (first CTA, whole row from L2/global): radix descent over the ordered keys of the
+  //      boundary bin ----------------------------------------------------------------------------
+  if (crank == 0) {
+    auto key_in_edge = [&](int i, uint32_t& key) -> bool {
+      const float v = __ldg(row + i);
+      key = float_to_ordered(v);
+      return bin_of(v) == edge;
+    };
+    const int sweeps = (len + kSelThreads - 1) / kSelThreads;
+    uint32_t prefix = 0, mask = 0, k_rem = need;
 #pragma unroll 1
-  for (int pass = 0; pass < 3; ++pass) {
-    const int shift = pass == 0 ? 21 : (pass == 1 ? 10 : 0);
-    const int bits = pass == 2 ? 10 : 11;
-    const uint32_t nb = 1u << bits;
-    for (int i = tid; i < kSelBins; i += kSelThreads) sh.hist[i] = 0;
-    __syncthreads();
-    for (int i = tid; i < len; i += kSelThreads) {
-      uint32_t k;
-      if (key_in_edge(i, k) && (k & mask) == prefix) atomicAdd(&sh.hist[(k >> shift) & (nb - 1)], 1u);
+    for (int pass = 0; pass < 3; ++pass) {
+      const int shift = pass == 0 ? 21 : (pass == 1 ? 10 : 0);
+      const int bits = pass == 2 ? 10 : 11;
+      const uint32_t nb = 1u << bits;
+      for (int i = tid; i < kSelBins; i += kSelThreads) sh.tot[i] = 0;
+      __syncthreads();
+      for (int i = tid; i < len; i += kSelThreads) {
+        uint32_t k;
+        if (key_in_edge(i, k) && (k & mask) == prefix) atomicAdd(&sh.tot[(k >> shift) & (nb - 1)], 1u);
+      }
+      __syncthreads();
+      find_boundary_bin(sh, sh.tot, nb, k_rem);
+      prefix |= sh.digit << shift;
+      mask |= (nb - 1) << shift;
+      k_rem -= sh.above;
+      __syncthreads();
     }
-    __syncthreads();
-    find_boundary_bin(sh, nb, k_rem);
-    prefix |= sh.digit << shift;
-    mask |= (nb - 1) << shift;
-    k_rem -= sh.above;
-    __syncthreads();
-  }
-  const uint32_t thresh = prefix;             // key of the last selected element
-  const uint32_t n_gt = need - k_rem;         // boundary-bin elements strictly above it
-  const bool take_all_ties = sh.ties == k_rem;
-  for (int s = 0; s < sweeps; ++s) {
-    const int i = s * kSelThreads + tid;
-    uint32_t k = 0;
-    const bool in = i < len && key_in_edge(i, k);
-    const bool gt = in && k > thresh;
-    const bool eq = in && k == thresh;
-    const uint32_t m = __ballot_sync(0xffffffffu, gt);
-    if (m) {
-      uint32_t base = 0;
-      if (lane == 0) base = atomicAdd(&sh.cnt_gt2, __popc(m));
-      base = __shfl_sync(0xffffffffu, base, 0);
-      if (gt) {
-        const uint32_t pos = above + base + __popc(m & ((1u << lane) - 1));
+    const uint32_t thresh = prefix;             // key of the last selected element
+    const uint32_t n_gt = need - k_rem;         // boundary-bin elements strictly above it
+    const bool take_all_ties = sh.ties == k_rem;
+    for (int s = 0; s < sweeps; ++s) {
+      const int i = s * kSelThreads + tid;
+      uint32_t k = 0;
+      const bool in = i < len && key_in_edge(i, k);
+      const bool gt = in && k > thresh;
+      const bool eq = in && k == thresh;
+      const uint32_t m = __ballot_sync(0xffffffffu, gt);
+      if (m) {
+        uint32_t base = 0;
+        if (lane == 0) base = atomicAdd(&sh.cnt_gt2, __popc(m));
+        base = __shfl_sync(0xffffffffu, base, 0);
+        if (gt) {
+          const uint32_t pos = above + base + __popc(m & ((1u << lane) - 1));
+          if (pos < (uint32_t)kTopK) out_row[pos] = slot_of(i);
+        }
+      }
+      if (take_all_ties && eq) {
+        const uint32_t pos = above + n_gt + atomicAdd(&sh.cnt_eq, 1u);
         if (pos < (uint32_t)kTopK) out_row[pos] = slot_of(i);
       }
     }
-    if (take_all_ties && eq) {
-      const uint32_t pos = above + n_gt + atomicAdd(&sh.cnt_eq, 1u);
-      if (pos < (uint32_t)kTopK) out_row[pos] = slot_of(i);
+    if (!take_all_ties) {
+      // more elements equal the threshold than are needed: keep the lowest positions
+      uint32_t running = 0;
+      for (int s = 0; s < sweeps && running < k_rem; ++s) {
+        const int i = s * kSelThreads + tid;
+        uint32_t k = 0;
+        const bool eq = i < len && key_in_edge(i, k) && k == thresh;
+        const uint32_t inc2 = block_inclusive_scan(eq ? 1u : 0u, sh.warp_sums);
+        const uint32_t rank = running + inc2 - 1;
+        if (eq && rank < k_rem) out_row[above + n_gt + rank] = slot_of(i);
+        if (tid == kSelThreads - 1) sh.above = inc2;
+        __syncthreads();
+        running += sh.above;
+        __syncthreads();
+      }
     }
+    __syncthreads();
+    uint32_t gt_total = 0;
+    for (int r = 0; r < csize; ++r) gt_total += sh.peer_gt[r];
+    if (tid == 0 && (gt_total != above || sh.cnt_gt2 != n_gt)) raise_status(status, DSA_STATUS_TOPK_COUNT);
   }
-  if (!take_all_ties) {
-    // more elements equal the threshold than are needed: keep the lowest positions
-    uint32_t running = 0;
-    for (int s = 0; s < sweeps && running < k_rem; ++s) {
-      const int i = s * kSelThreads + tid;
-      uint32_t k = 0;
-      const bool eq = i < len && key_in_edge(i, k) && k == thresh;
-      const uint32_t incl = block_inclusive_scan(eq ? 1u : 0u, sh.warp_sums);
-      const uint32_t rank = running + incl - 1;
-      if (eq && rank < k_rem) out_row[above + n_gt + rank] = slot_of(i);
-      if (tid == kSelThreads - 1) sh.above = incl;
-      __syncthreads();
-      running += sh.above;
-      __syncthreads();
-    }
-  }
-  __syncthreads();
-  if (tid == 0 && (sh.cnt_gt != above || sh.cnt_gt2 != n_gt)) raise_status(status, DSA_STATUS_TOPK_COUNT);
+  cluster.sync();
+}
+
+// CTAs per request: as many as fit in one wave (a CTA of 1024 threads owns an SM).
+static int select_cluster_size(int batch) {
+  const int sms = sm_count();
+  if (batch * 4 <= sms) return 4;
+  if (batch * 2 <= sms) return 2;
+  return 1;
 }
 
 cudaError_t launch_topk_select(const float* scores, int64_t score_stride, const int32_t* seq_lens,
@@ -316,11 +375,22 @@ cudaError_t launch_topk_select(const float* scores, int64_t score_stride, const 
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  size_t smem = sizeof(float) * (size_t)min(kSelRowCap, max(max_pages * kPage, 1));
-  topk_select_kernel<<<batch, kSelThreads, smem, stream>>>(scores, score_stride, seq_lens,
-                                                           block_table, bt_stride, out, out_stride,
-                                                           max_pages, status);
-  return cudaGetLastError();
+  const int csize = select_cluster_size(batch);
+  const int seg_max = (((max_pages * kPage + csize - 1) / csize) + 3) & ~3;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(batch * csize));
+  cfg.blockDim = dim3(kSelThreads);
+  cfg.dynamicSmemBytes = sizeof(float) * (size_t)min(kSelRowCap, max(seg_max, 4));
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = csize;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, topk_select_kernel, scores, score_stride, seq_lens, block_table,
+                            bt_stride, out, out_stride, max_pages, status);
 }
 
 }  // namespace dsa
