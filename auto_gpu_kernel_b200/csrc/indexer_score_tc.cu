@@ -88,6 +88,7 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
   TcShared& sh = *reinterpret_cast<TcShared*>(base + kTcStages * kTileDataBytes + 2 * kPageDataBytes);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  ptx::launch_dependents();  // the selection kernel may be scheduled as SMs free up; it waits for our scores
 
   // ---- tiles per request -> exclusive prefix (all threads) ------------------------------------
   {

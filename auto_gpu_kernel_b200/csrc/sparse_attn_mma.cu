@@ -158,6 +158,7 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
     a = k0 < topk ? __ldg(indices + (size_t)tt * index_stride + k0) : -1;
     b = k1 < topk ? __ldg(indices + (size_t)tt * index_stride + k1) : -1;
   };
+  ptx::grid_dependency_wait();  // the index rows may come from the kernel before us in the stream
   load_indices(ti, ji, nv0, nv1);
   const int sub = lane >> 3, ch = lane & 7;  // row inside a 4-row group, 16-byte chunk of a 128-byte block
   auto issue_tile = [&]() {
@@ -410,12 +411,22 @@ cudaError_t launch_sparse_attn_mma(const void* q_nope, const void* q_pe, const v
     attr_set = true;
   }
   const AtPlan plan = at_make_plan(tokens, topk, sm_count());
-  sparse_attn_mma_kernel<<<plan.grid, kMmThreads, kMmDynBytes, stream>>>(
-      static_cast<const __nv_bfloat16*>(q_nope), static_cast<const __nv_bfloat16*>(q_pe),
-      static_cast<const __nv_bfloat16*>(ckv), static_cast<const __nv_bfloat16*>(kpe), indices,
-      index_stride, sm_scale * kMmLog2e, static_cast<__nv_bfloat16*>(out), lse, tokens, topk,
-      num_slots, plan, ws, status);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)plan.grid);
+  cfg.blockDim = dim3(kMmThreads);
+  cfg.dynamicSmemBytes = kMmDynBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, sparse_attn_mma_kernel, static_cast<const __nv_bfloat16*>(q_nope),
+                            static_cast<const __nv_bfloat16*>(q_pe),
+                            static_cast<const __nv_bfloat16*>(ckv),
+                            static_cast<const __nv_bfloat16*>(kpe), indices, index_stride,
+                            sm_scale * kMmLog2e, static_cast<__nv_bfloat16*>(out), lse, tokens, topk,
+                            num_slots, plan, ws, status);
 }
 
 }  // namespace dsa

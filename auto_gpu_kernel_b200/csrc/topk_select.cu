@@ -21,6 +21,7 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include "ptx.cuh"
 #include "tmap.cuh"
 
 namespace dsa {
@@ -132,6 +133,10 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   const int seg_len = seg_hi - seg_lo;
   const bool staged = seg <= kSelRowCap;
   auto value_at = [&](int i) -> float { return staged ? row_s[i - seg_lo] : __ldg(row + i); };
+
+  // everything above only read the caller's inputs; the scores come from the kernel before us
+  ptx::launch_dependents();
+  ptx::grid_dependency_wait();
 
   // ---- sweep A: stage the segment, min / max ----------------------------------------------------
   {
@@ -382,13 +387,15 @@ cudaError_t launch_topk_select(const float* scores, int64_t score_stride, const 
   cfg.blockDim = dim3(kSelThreads);
   cfg.dynamicSmemBytes = sizeof(float) * (size_t)min(kSelRowCap, max(seg_max, 4));
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = csize;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   return cudaLaunchKernelEx(&cfg, topk_select_kernel, scores, score_stride, seq_lens, block_table,
                             bt_stride, out, out_stride, max_pages, status);
 }
