@@ -143,8 +143,9 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
   const int g = lane >> 2, t4 = lane & 3;
   const int tpt = plan.tiles_per_token;
   const long total = (long)tokens * tpt;
-  const long w0 = (long)blockIdx.x * plan.per_cta;
-  const long w1 = w0 + plan.per_cta < total ? w0 + plan.per_cta : total;
+  const long w0 = plan.balanced ? plan.starts[blockIdx.x] : (long)blockIdx.x * plan.per_cta;
+  const long w1 = plan.balanced ? plan.starts[blockIdx.x + 1]
+                                : (w0 + plan.per_cta < total ? w0 + plan.per_cta : total);
   const int n = (int)(w1 - w0);
   if (n <= 0) return;
   AtPartials part = at_carve(ws_raw, tokens, plan.segs_max);
@@ -350,7 +351,8 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
 #pragma unroll
       for (int ww = 0; ww < 8; ++ww) { lt0 += sh.red[ww][g]; lt1 += sh.red[ww][g + 8]; }
       const long first_tile = t * tpt, last_tile = first_tile + tpt - 1;
-      const int cta_first = (int)(first_tile / plan.per_cta), cta_last = (int)(last_tile / plan.per_cta);
+      const int cta_first = plan.balanced ? at_owner(plan, first_tile) : (int)(first_tile / plan.per_cta);
+      const int cta_last = plan.balanced ? at_owner(plan, last_tile) : (int)(last_tile / plan.per_cta);
       const int n_seg = cta_last - cta_first + 1, seg = (int)blockIdx.x - cta_first;
       const int col = 64 * w + 2 * t4;
       if (n_seg == 1) {
