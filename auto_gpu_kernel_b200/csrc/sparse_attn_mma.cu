@@ -15,7 +15,8 @@
 //   * three 64-row stages in shared memory, filled by cp.async 16-byte copies issued by all warps
 //     two tiles ahead; a tile is nine [64 rows x 128 B] blocks (8 ckv column blocks + kpe) with the
 //     16-byte chunks of a row XOR-swizzled by (row & 7), so both ldmatrix patterns below are
-//     conflict-free; masked rows (-1) are zero-filled.  (Fetching rows with cp.async.bulk, 1024 B +
+//     conflict-free; masked rows (-1) are zero-filled.  (An L2 prefetch stream of bulk prefetches a
+//     few tiles ahead was tried on top: 56-69 us instead of 42-44 us.)  (Fetching rows with cp.async.bulk, 1024 B +
 //     128 B per row into linear padded rows, was measured at 92.7 us for the headline shape against
 //     50.5 us for these 16-byte copies: the bulk engine costs ~70 cycles per request.);
 //   * S[16 heads, 64 rows] = Q.K^T: warp w owns rows 8w..8w+7; q lives in registers as the 36
@@ -27,7 +28,7 @@
 //     tile, read with ldmatrix.x4.trans; accumulators stay in registers;
 //   * the (token, tile) sequence is cut into equal contiguous ranges, one per CTA; tokens covered by
 //     several CTAs leave partials in the workspace and are merged by the CTA that arrives last.
-#include <cuda_pipeline_primitives.h>
+#include <cstdlib>
 
 #include "attn_plan.cuh"
 #include "common.cuh"
@@ -412,7 +413,15 @@ cudaError_t launch_sparse_attn_mma(const void* q_nope, const void* q_pe, const v
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  const AtPlan plan = at_make_plan(tokens, topk, sm_count());
+  AtPlan plan = at_make_plan(tokens, topk, sm_count());
+  // The cost-balanced split was measured equal to the uniform one at the headline shape (42.3 vs
+  // 41.7 us): the slow CTAs are slow per tile, not by token starts.  DSA_ATT_BALANCED=1 enables it.
+  static int balanced = -1;
+  if (balanced < 0) {
+    const char* e = getenv("DSA_ATT_BALANCED");
+    balanced = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  if (!balanced) plan.balanced = 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)plan.grid);
   cfg.blockDim = dim3(kMmThreads);
@@ -420,7 +429,7 @@ cudaError_t launch_sparse_attn_mma(const void* q_nope, const void* q_pe, const v
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled();
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, sparse_attn_mma_kernel, static_cast<const __nv_bfloat16*>(q_nope),

@@ -7,6 +7,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 namespace dsa {
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -40,6 +42,18 @@ inline bool make_tmap_2d_sw128(CUtensorMap* map, CUtensorMapDataType type, int e
   return enc(map, type, 2, const_cast<void*>(base), dims, strides, box, estr,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Programmatic dependent launch between the kernels of one operator chain is on by default;
+// DSA_PDL=0 launches them strictly serialised (use it when timing kernels one by one: with PDL a
+// dependent kernel's duration includes the time it waits for its predecessor).
+inline int pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("DSA_PDL");
+    on = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return on;
 }
 
 inline int sm_count() {
