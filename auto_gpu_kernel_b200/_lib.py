@@ -46,8 +46,21 @@ _lib = None
 
 
 def library_path() -> Path:
+    """DSA_B200_LIB if set; else next to this file; else, when that directory is read-only (a
+    solution unpacked by an evaluator), a per-source-digest directory under the temp dir."""
     override = os.environ.get("DSA_B200_LIB")
-    return Path(override) if override else _build.PKG_DIR / _build.LIB_NAME
+    if override:
+        return Path(override)
+    if os.access(_build.PKG_DIR, os.W_OK):
+        return _build.PKG_DIR / _build.LIB_NAME
+    import hashlib
+    import tempfile
+    digest = hashlib.sha256()
+    for src in sorted(_build.CSRC.glob("*.cu*")) + sorted(_build.INCLUDE.glob("*.h")):
+        digest.update(src.read_bytes())
+    out = Path(tempfile.gettempdir()) / f"dsa_b200_{digest.hexdigest()[:16]}"
+    out.mkdir(parents=True, exist_ok=True)
+    return out / _build.LIB_NAME
 
 
 def load(build_if_missing: bool = True):
