@@ -40,6 +40,9 @@ SIGNATURES = {
     "dsa_sparse_attn_cuda_core": (_c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _c_float, _ptr,
                                            _ptr, _c_int, _c_int, _c_int, _c_i64, _ptr, _c_size,
                                            _ptr, _ptr]),
+    "dsa_index_cache_write": (_c_int, [_ptr, _c_int, _c_i64, _ptr, _ptr, _c_int, _c_int, _ptr, _ptr]),
+    "dsa_kv_cache_append": (_c_int, [_ptr, _c_i64, _ptr, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64,
+                                     _ptr, _ptr]),
 }
 
 _lib = None

@@ -24,6 +24,10 @@ cudaError_t launch_sparse_attn_mma(const void*, const void*, const void*, const 
                                    const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
                                    void*, int32_t*, cudaStream_t);
 int att_pick_splits(int tokens, int topk);
+cudaError_t launch_index_cache_write(const void*, int, int64_t, const int32_t*, void*, int, int64_t,
+                                     int32_t*, cudaStream_t);
+cudaError_t launch_kv_cache_append(const void*, int64_t, const void*, int64_t, const int32_t*, void*,
+                                   void*, int, int64_t, int32_t*, cudaStream_t);
 size_t att_workspace_bytes(int tokens, int splits);
 }  // namespace dsa
 
@@ -194,6 +198,36 @@ int dsa_sparse_attn_tcgen05(const void* q_nope, const void* q_pe, const void* ck
                             int32_t* status_dev, void* stream) {
   return attn_impl(q_nope, q_pe, ckv, kpe, sparse_indices, index_stride, sm_scale, out, lse, tokens,
                    heads, topk, num_slots, workspace, workspace_bytes, status_dev, stream, 2);
+}
+
+int dsa_index_cache_write(const void* keys, int key_dtype, int64_t key_stride, const int32_t* slots,
+                          void* k_cache, int tokens, int num_pages, int32_t* status_dev,
+                          void* stream) {
+  if (tokens == 0) return DSA_OK;
+  if (!keys || !slots || !k_cache) return DSA_ERR_NULL_POINTER;
+  if (tokens < 0 || num_pages <= 0 || key_stride < dsa::kIdxDim || (key_dtype != 0 && key_dtype != 1))
+    return DSA_ERR_BAD_SHAPE;
+  const int64_t elem = key_dtype == 0 ? 4 : 2;
+  if (!aligned16(keys) || (key_stride * elem) % 16 != 0 || !aligned16(k_cache))
+    return DSA_ERR_MISALIGNED;
+  return static_cast<int>(dsa::launch_index_cache_write(
+      keys, key_dtype, key_stride, slots, k_cache, tokens,
+      static_cast<int64_t>(num_pages) * dsa::kPage, status_dev, static_cast<cudaStream_t>(stream)));
+}
+
+int dsa_kv_cache_append(const void* ckv, int64_t ckv_stride, const void* kpe, int64_t kpe_stride,
+                        const int32_t* slots, void* ckv_cache, void* kpe_cache, int tokens,
+                        int64_t num_slots, int32_t* status_dev, void* stream) {
+  if (tokens == 0) return DSA_OK;
+  if (!ckv || !kpe || !slots || !ckv_cache || !kpe_cache) return DSA_ERR_NULL_POINTER;
+  if (tokens < 0 || num_slots <= 0 || ckv_stride < dsa::kCkv || kpe_stride < dsa::kKpe)
+    return DSA_ERR_BAD_SHAPE;
+  if (!aligned16(ckv) || !aligned16(kpe) || !aligned16(ckv_cache) || !aligned16(kpe_cache) ||
+      ckv_stride % 8 != 0 || kpe_stride % 8 != 0)
+    return DSA_ERR_MISALIGNED;
+  return static_cast<int>(dsa::launch_kv_cache_append(ckv, ckv_stride, kpe, kpe_stride, slots,
+                                                      ckv_cache, kpe_cache, tokens, num_slots,
+                                                      status_dev, static_cast<cudaStream_t>(stream)));
 }
 
 }  // extern "C"

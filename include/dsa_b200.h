@@ -158,6 +158,31 @@ int dsa_sparse_attn_cuda_core(const void* q_nope, const void* q_pe, const void* 
                               int64_t num_slots, void* workspace, size_t workspace_bytes,
                               int32_t* status_dev, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Cache writers: the producers of the two paged caches, run on the step before the path.
+ * The reference has no writer (its inputs arrive packed); the layouts are the ones its readers
+ * unpack: index-key pages by dequant_fp8_kv_cache (archive/dsa_topk_indexer_fp8_h64_d128_topk2048_ps64/
+ * solution/triton/indexer_baseline.py:16-36; layout notes in that directory's CLAUDE.md:65), ckv/kpe
+ * rows by the flat views of .../sparse_baseline.py:18-28.
+ *
+ * dsa_index_cache_write: per token t with slot = slots[t] (page * 64 + position; -1 = skip):
+ *   scale = max(max_d |key[t,d]|, 1e-12) / 448;  byte[d] = e4m3(key[t,d] / scale) (round to nearest
+ *   even, saturating);  the 128 bytes go to page*8448 + position*128, the fp32 scale to
+ *   page*8448 + 8192 + position*4.
+ *   keys [tokens,128], row stride `key_stride` elements, key_dtype 0 = fp32, 1 = bf16.
+ * dsa_kv_cache_append: ckv_cache[slot,:] = ckv[t,:] (512 bf16), kpe_cache[slot,:] = kpe[t,:]
+ *   (64 bf16); row strides in elements (multiples of 8).
+ * Slots outside the cache are skipped and reported as DSA_STATUS_BAD_SLOT.  Two tokens with the
+ * same slot in one call race (the result is one of them).
+ * ------------------------------------------------------------------------------------------- */
+int dsa_index_cache_write(const void* keys, int key_dtype, int64_t key_stride, const int32_t* slots,
+                          void* k_cache, int tokens, int num_pages, int32_t* status_dev,
+                          void* stream);
+
+int dsa_kv_cache_append(const void* ckv, int64_t ckv_stride, const void* kpe, int64_t kpe_stride,
+                        const int32_t* slots, void* ckv_cache, void* kpe_cache, int tokens,
+                        int64_t num_slots, int32_t* status_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

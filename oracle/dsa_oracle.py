@@ -76,6 +76,54 @@ def dequant_index_pages(k_index_cache_fp8: torch.Tensor, pages: torch.Tensor | N
     return data * scale.unsqueeze(-1)
 
 
+# ----------------------------------------------------------------------------------------------
+# Cache writers (the producers of the inputs above).  The reference ships no writer; this restates
+# the layout its reader (indexer_baseline.py:16-36) unpacks, with the e4m3 rounding written out.
+# ----------------------------------------------------------------------------------------------
+def quantize_e4m3fn(values: np.ndarray) -> np.ndarray:
+    """float32 -> e4m3fn code (uint8): round to nearest, ties to the even code, saturating at 448."""
+    table = e4m3fn_table()
+    pos = table[:0x7F].astype(np.float64)                 # codes 0x00..0x7e: 0 .. 448, ascending
+    mag = np.minimum(np.abs(values.astype(np.float64)), 448.0)
+    hi = np.clip(np.searchsorted(pos, mag, side="left"), 1, len(pos) - 1)
+    lo = hi - 1
+    d_lo, d_hi = mag - pos[lo], pos[hi] - mag
+    pick_hi = (d_hi < d_lo) | ((d_hi == d_lo) & (hi % 2 == 0))
+    code = np.where(pick_hi, hi, lo).astype(np.uint8)
+    code = np.where(mag == 0.0, 0, code).astype(np.uint8)
+    sign = (np.signbit(values).astype(np.uint8) << 7)
+    return code | sign
+
+
+def write_index_keys(keys: torch.Tensor, slots: torch.Tensor, k_index_cache_fp8: torch.Tensor):
+    """Quantise keys [n,128] per token (scale = max(absmax, 1e-12) / 448, data = e4m3(key / scale))
+    and store token t at global slot slots[t] (-1 skips) of the packed pages, in place."""
+    raw = k_index_cache_fp8.view(torch.uint8).reshape(k_index_cache_fp8.shape[0], PAGE_BYTES)
+    k = keys.to(torch.float32).numpy()
+    amax = np.maximum(np.abs(k).max(axis=1), np.float32(1e-12)).astype(np.float32)
+    scale = (amax / np.float32(448.0)).astype(np.float32)
+    codes = quantize_e4m3fn((k / scale[:, None]).astype(np.float32))
+    for t, slot in enumerate(slots.tolist()):
+        if slot < 0:
+            continue
+        page, pos = divmod(slot, PAGE_SIZE)
+        raw[page, pos * INDEX_DIM:(pos + 1) * INDEX_DIM] = torch.from_numpy(codes[t])
+        at = PAGE_DATA_BYTES + 4 * pos
+        raw[page, at:at + 4] = torch.from_numpy(scale[t:t + 1].view(np.uint8))
+    return k_index_cache_fp8
+
+
+def append_kv(ckv, kpe, slots, ckv_cache, kpe_cache):
+    """ckv_cache.flat[slot] = ckv[t], kpe_cache.flat[slot] = kpe[t] for slot = slots[t] >= 0 (the
+    flat views of sparse_baseline.py:18-19), in place."""
+    flat_c = ckv_cache.view(-1, ckv_cache.shape[-1])
+    flat_p = kpe_cache.view(-1, kpe_cache.shape[-1])
+    keep = slots >= 0
+    flat_c[slots[keep].long()] = ckv[keep]
+    flat_p[slots[keep].long()] = kpe[keep]
+    return ckv_cache, kpe_cache
+
+
 @torch.no_grad()
 def indexer_scores(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table):
     """Per-request fp32 score rows, list of 1-D tensors of length seq_len[b].

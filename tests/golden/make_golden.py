@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this directory by running the REFERENCE repository's own two
 PyTorch definitions on CPU.  Run once, in a container where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [--only=cache_write]
 
 It imports (read-only, by file path)
   archive/dsa_topk_indexer_fp8_h64_d128_topk2048_ps64/solution/triton/indexer_baseline.py::kernel
@@ -68,8 +68,47 @@ def attention_case(ref, name, seq_lens, seed, pad_tail=0, blank_row=None):
     print(name, "valid per token", (inp.sparse_indices >= 0).sum(dim=1).tolist())
 
 
+def cache_write_case(ref, name, seed):
+    """Keys -> packed pages.  The reference has no writer, so the expected bytes come from the
+    plain torch formulation of the layout its reader unpacks (absmax / 448 scale, torch's e4m3
+    cast), and the reference's own dequant_fp8_kv_cache of those bytes pins the reader's view."""
+    gen = torch.Generator().manual_seed(seed)
+    pages, n = 5, 203
+    keys = torch.randn(n, wl.INDEX_DIM, generator=gen)
+    keys[0] = 0.0                                            # all-zero token: scale from the clamp
+    keys[1] *= torch.logspace(-8, 2, wl.INDEX_DIM)           # wide range: e4m3 subnormals and zeros
+    keys[2] = -keys[2].abs()                                 # maximum is negative
+    keys[3] = 448.0 * torch.linspace(-1, 1, wl.INDEX_DIM)    # exact code points and ties
+    keys[4, 1:] = keys[4, 0] * 1e-3
+    slots = torch.randperm(pages * wl.PAGE_SIZE, generator=gen)[:n].to(torch.int32)
+    slots[7] = -1                                            # not cached
+    cache = torch.zeros(pages, wl.PAGE_BYTES, dtype=torch.uint8)
+    amax = keys.abs().amax(dim=-1).clamp_min(1e-12)
+    scale = (amax / wl.FP8_MAX).to(torch.float32)
+    data = (keys / scale.unsqueeze(-1)).to(torch.float8_e4m3fn).view(torch.uint8)
+    for t in range(n):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        pg, pos = divmod(s, wl.PAGE_SIZE)
+        cache[pg, pos * wl.INDEX_DIM:(pos + 1) * wl.INDEX_DIM] = data[t]
+        cache[pg, wl.PAGE_SIZE * wl.INDEX_DIM + 4 * pos: wl.PAGE_SIZE * wl.INDEX_DIM + 4 * pos + 4] = \
+            scale[t:t + 1].view(torch.uint8)
+    packed = cache.view(torch.int8).reshape(pages, wl.PAGE_SIZE, 1, wl.INDEX_DIM + 4)
+    dense = ref.dequant_fp8_kv_cache(packed)                 # [pages,64,128] fp32
+    np.savez_compressed(HERE / f"{name}.npz", keys=keys.numpy(), slots=slots.numpy(),
+                        cache_i8=packed.numpy(), dequant=dense.numpy())
+    print(name, "tokens", n, "pages", pages)
+
+
 def main():
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    args = [a for a in sys.argv[1:] if not a.startswith("--only=")]
+    only = [a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--only=")]
+    root = Path(args[0] if args else "/root/reference")
+    if only == ["cache_write"]:
+        idx_ref = _load(root / IDX_REL, "ref_indexer_baseline")
+        cache_write_case(idx_ref, "cache_write", seed=5)
+        return
     torch.manual_seed(0)
     idx_ref = _load(root / IDX_REL, "ref_indexer_baseline")
     att_ref = _load(root / ATT_REL, "ref_sparse_baseline")
@@ -82,6 +121,8 @@ def main():
     # Attention with forced tail padding and one fully masked row (lse=-inf, NaN output in the
     # reference; recorded as produced).
     attention_case(att_ref, "attention_padded", [300, 256, 64], seed=3, pad_tail=1900, blank_row=2)
+    # Cache writer: keys -> packed pages, read back by the reference's dequantiser.
+    cache_write_case(idx_ref, "cache_write", seed=5)
 
 
 if __name__ == "__main__":
