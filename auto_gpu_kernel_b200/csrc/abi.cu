@@ -24,6 +24,10 @@ cudaError_t launch_sparse_attn_mma(const void*, const void*, const void*, const 
                                    const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
                                    void*, int32_t*, cudaStream_t);
 int att_pick_splits(int tokens, int topk);
+cudaError_t launch_indexer_score_prefill(const void*, const void*, const float*, const int32_t*,
+                                         const int32_t*, float*, int64_t, int, int, int, int,
+                                         int32_t*, cudaStream_t);
+constexpr int kPrefillMinRows = 16;   // below this the per-row streaming kernel is as fast
 cudaError_t launch_index_cache_write(const void*, int, int64_t, const int32_t*, void*, int, int64_t,
                                      int32_t*, cudaStream_t);
 cudaError_t launch_kv_cache_append(const void*, int64_t, const void*, int64_t, const int32_t*, void*,
@@ -82,7 +86,12 @@ static int scores_impl(const void* q_fp8, const void* k_cache, const float* weig
     e = dsa::launch_indexer_score_simt(q_fp8, k_cache, weights, seq_lens, block_table,
                                        block_table_stride, scores, score_stride, batch, num_pages,
                                        max_pages, status_dev, s);
-  } else if (variant == 0) {
+  } else if (variant == 0 && block_table_stride == 0 && batch >= dsa::kPrefillMinRows) {
+    // every row reads the same pages (chunked prefill): four rows share each tcgen05.mma
+    e = dsa::launch_indexer_score_prefill(q_fp8, k_cache, weights, seq_lens, block_table, scores,
+                                          score_stride, batch, num_pages, max_pages, skip_short,
+                                          status_dev, s);
+  } else if (variant == 0 || variant == 2) {
     e = dsa::launch_indexer_score_tc(q_fp8, k_cache, weights, seq_lens, block_table,
                                      block_table_stride, scores, score_stride, batch, num_pages,
                                      max_pages, skip_short, status_dev, s);

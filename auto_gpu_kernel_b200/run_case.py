@@ -5,6 +5,7 @@
     python -m auto_gpu_kernel_b200.run_case indexer   --batch 64 --context 32768
     python -m auto_gpu_kernel_b200.run_case attention --batch 64 --context 8192 --variant 0
     python -m auto_gpu_kernel_b200.run_case block     --batch 64 --context 32768
+    python -m auto_gpu_kernel_b200.run_case prefill   --batch 4096 --context 16384
 
 Meant for profilers (the launches of one kernel in a small process) and for quick A/B timing.
 The time printed is CUDA-event time over `--iters` back-to-back launches after `--warmup` ones.
@@ -21,13 +22,14 @@ import sys
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("case", choices=["scorer", "select", "indexer", "attention", "block"])
+    ap.add_argument("case", choices=["scorer", "select", "indexer", "attention", "block", "prefill"])
     ap.add_argument("--batch", type=int, default=64, help="requests (= query tokens)")
     ap.add_argument("--context", type=int, default=32768, help="tokens per request")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--variant", type=int, default=0,
-                    help="scorer: 0 tcgen05, 1 CUDA-core; attention: 0 mma.sync, 1 CUDA-core, 2 tcgen05")
+                    help="scorer/prefill: 0 tcgen05, 1 CUDA-core, 2 streaming tcgen05 kernel; "
+                         "attention: 0 mma.sync, 1 CUDA-core, 2 tcgen05")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-pdl", action="store_true")
     args = ap.parse_args(argv)
@@ -57,6 +59,15 @@ def main(argv=None) -> int:
             topk = torch.empty(args.batch, indexer.TOPK, dtype=torch.int32, device=dev)
             fn = lambda: indexer.kernel(*a, topk)
         moved = inp.k_index_cache_fp8.numel()
+    elif args.case == "prefill":
+        # chunked prefill: `batch` query rows after a prefix of `context` tokens, all rows reading
+        # the same pages (block_table row stride 0); row i sees context + i + 1 tokens
+        inp = wl.make_shared_prefix_indexer_inputs(args.context, args.batch, seed=args.seed, device=dev)
+        shared = inp.block_table[:1].expand(args.batch, -1)
+        a = (inp.q_index_fp8, inp.k_index_cache_fp8, inp.weights, inp.seq_lens, shared)
+        out = indexer.scores(*a, variant=args.variant)
+        fn = lambda: indexer.scores(*a, variant=args.variant, out=out)
+        moved = int(inp.seq_lens.sum()) * 2 * 64 * 128   # flops, reported in the gb_per_s field as GFLOP/s
     elif args.case == "attention":
         inp = wl.make_attention_inputs(lens, seed=args.seed, device=dev)
         out = torch.empty_like(inp.q_nope)

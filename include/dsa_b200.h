@@ -106,8 +106,10 @@ int dsa_indexer_topk_noalloc(const void* q_fp8, const void* k_cache, const float
 
 /* Stage 1 alone: fp32 score rows, scores[b*score_stride + t] for t < seq_len[b] (the quantity
  * `final_scores` of indexer_baseline.py:80).  Entries t >= seq_len[b] are left untouched.
- * `variant`: 0 = tensor-core (tcgen05) scorer, 1 = plain CUDA-core scorer kept as an on-device
- * cross-check. */
+ * `variant`: 0 = tensor-core (tcgen05) scorer -- the streaming kernel (one row per product), or,
+ * when block_table_stride == 0 and batch >= 16 (chunked prefill: every row reads the same pages),
+ * the kernel that shares each key tile among eight rows; 1 = plain CUDA-core scorer kept as an
+ * on-device cross-check; 2 = the streaming tcgen05 kernel whatever the shape. */
 int dsa_indexer_scores(const void* q_fp8, const void* k_cache, const float* weights,
                        const int32_t* seq_lens, const int32_t* block_table,
                        int64_t block_table_stride, float* scores, int64_t score_stride,

@@ -125,6 +125,44 @@ def test_shared_block_table_rows_prefill(cuda):
         assert set(out_a[r].tolist()) == set(out_b[r].tolist())
 
 
+@pytest.mark.parametrize("prefix_len,chunk_len", [(3000, 96), (5000, 37), (200, 300), (0, 17)])
+def test_prefill_scorer_matches_oracle_and_streaming_kernel(cuda, prefix_len, chunk_len):
+    """The shared-pages scorer (eight rows per key tile, N = 256 products) against the oracle and
+    against the streaming tcgen05 kernel: chunk sizes that are not multiples of 8, rows shorter
+    than one tile, a prefix of zero."""
+    inp = wl.make_shared_prefix_indexer_inputs(prefix_len=prefix_len, chunk_len=chunk_len, seed=6,
+                                               device=cuda)
+    shared = inp.block_table[:1].expand(chunk_len, -1)
+    lens = inp.seq_lens.tolist()
+    rows = [r.cpu() for r in oracle.indexer_scores(*inp.args())]
+    got_pf = indexer.scores(inp.q_index_fp8, inp.k_index_cache_fp8, inp.weights, inp.seq_lens,
+                            shared, variant=0)
+    got_st = indexer.scores(inp.q_index_fp8, inp.k_index_cache_fp8, inp.weights, inp.seq_lens,
+                            shared, variant=2)
+    workspace.check_status(cuda)
+    assert _score_err(got_pf, rows, lens) < SCORE_RTOL
+    assert _score_err(got_st, rows, lens) < SCORE_RTOL
+    for b, n in enumerate(lens):   # untouched beyond each row's length
+        assert torch.isnan(got_pf[b, n:]).all()
+
+
+def test_prefill_scorer_ragged_lengths(cuda):
+    """Rows of one launch need not be causal: arbitrary lengths over the shared pages, including
+    empty rows and rows at the top-k boundary."""
+    inp = wl.make_shared_prefix_indexer_inputs(prefix_len=6000, chunk_len=40, seed=8, device=cuda)
+    lens = [6040, 0, 1, 2048, 2049, 127, 128, 129, 6000, 64] * 4
+    seq = torch.tensor(lens, dtype=torch.int32, device=cuda)
+    shared = inp.block_table[:1].expand(40, -1)
+    args = (inp.q_index_fp8, inp.k_index_cache_fp8, inp.weights, seq)
+    rows = [r.cpu() for r in oracle.indexer_scores(*args, inp.block_table)]
+    got = indexer.scores(*args, shared, variant=0)
+    assert _score_err(got, rows, lens) < SCORE_RTOL
+    out = indexer.run(*args, shared)
+    workspace.check_status(cuda)
+    ragged = wl.IndexerInputs(inp.q_index_fp8, inp.k_index_cache_fp8, inp.weights, seq, inp.block_table)
+    assert_topk_matches(ragged, out, rows, label="prefill ragged")
+
+
 def test_cpu_tensors_are_rejected():
     inp = wl.make_indexer_inputs([100], seed=0)
     with pytest.raises(RuntimeError, match="no CPU path"):
