@@ -32,11 +32,11 @@ def write_index_keys(keys, slots, k_index_cache_fp8):
         raise ValueError("k_index_cache_fp8 must be a contiguous [P,64,1,132] int8 tensor")
     dev = keys.device
     lib = _lib.load()
-    with torch.cuda.device(dev):
+    with workspace.device_guard(dev):
         rc = lib.dsa_index_cache_write(
             keys.data_ptr(), 0 if keys.dtype == torch.float32 else 1, keys.stride(0),
             slots.data_ptr(), cache.data_ptr(), keys.shape[0], cache.shape[0],
-            workspace.status_word(dev).data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+            workspace.status_word(dev).data_ptr(), workspace.stream_handle(dev))
     _lib.check(rc, "dsa_index_cache_write")
 
 
@@ -60,9 +60,9 @@ def append_kv(ckv, kpe, slots, ckv_cache, kpe_cache):
         raise ValueError("ckv_cache and kpe_cache hold different numbers of slots")
     dev = ckv.device
     lib = _lib.load()
-    with torch.cuda.device(dev):
+    with workspace.device_guard(dev):
         rc = lib.dsa_kv_cache_append(
             ckv.data_ptr(), ckv.stride(0), kpe.data_ptr(), kpe.stride(0), slots.data_ptr(),
             ckv_cache.data_ptr(), kpe_cache.data_ptr(), n, num_slots,
-            workspace.status_word(dev).data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+            workspace.status_word(dev).data_ptr(), workspace.stream_handle(dev))
     _lib.check(rc, "dsa_kv_cache_append")

@@ -41,7 +41,7 @@ struct AtPartials {
 };
 
 __host__ __device__ inline size_t at_counter_bytes(int tokens) {
-  return (((size_t)tokens * 4 + 255) / 256) * 256;
+  return attn_counter_region_bytes(tokens);
 }
 __host__ __device__ inline AtPartials at_carve(void* ws, int tokens, int segs_max) {
   AtPartials w;
@@ -56,7 +56,7 @@ __host__ __device__ inline AtPartials at_carve(void* ws, int tokens, int segs_ma
   return w;
 }
 
-inline AtPlan at_make_plan(int tokens, int topk, int sms) {
+inline AtPlan at_make_plan(int tokens, int topk, int sms, double start_cost = 1.0) {
   AtPlan p;
   p.tiles_per_token = (topk + kAtTile - 1) / kAtTile;
   const long total = (long)tokens * p.tiles_per_token;
@@ -79,7 +79,7 @@ inline AtPlan at_make_plan(int tokens, int topk, int sms) {
   if (p.segs_max > 1 && p.grid <= kAtMaxGrid && p.per_cta >= 4) {
     // cost of a token = its tiles + 1 (the token start); cut the cost axis into `grid` equal parts
     const int tpt = p.tiles_per_token;
-    const double token_cost = tpt + 1.0, budget = tokens * token_cost / p.grid;
+    const double token_cost = tpt + start_cost, budget = tokens * token_cost / p.grid;
     int worst = 1, segs_of_token = 0;
     long prev_token = -1;
     p.starts[0] = 0;
@@ -87,7 +87,7 @@ inline AtPlan at_make_plan(int tokens, int topk, int sms) {
       const double x = budget * c;
       const long t = (long)(x / token_cost);
       const double rem = x - t * token_cost;
-      long w = t * tpt + (rem <= 1.0 ? 0 : (long)(rem - 1.0 + 0.999999));
+      long w = t * tpt + (rem <= start_cost ? 0 : (long)(rem - start_cost + 0.999999));
       if (w <= p.starts[c - 1]) w = p.starts[c - 1] + 1;
       if (w > total - (p.grid - c)) w = total - (p.grid - c);
       p.starts[c] = (int)w;

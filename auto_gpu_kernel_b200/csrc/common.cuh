@@ -40,6 +40,15 @@ __device__ __forceinline__ uint32_t float_to_ordered(float f) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+// Size of the per-token arrival-counter region at the start of every attention workspace layout.
+// The counters must be zero between calls (the last arriver resets its own), so no layout may ever
+// put partial results where another call's counters live: the region has one fixed size for every
+// token count that uses counters at all (splitting a token over CTAs stops far below 4096 tokens).
+__host__ __device__ inline size_t attn_counter_region_bytes(int tokens) {
+  const size_t need = (((size_t)tokens * 4 + 255) / 256) * 256;
+  return need < 16384 ? 16384 : need;
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -26,8 +26,14 @@
 //     memory so that every warp sees all 64 rows;
 //   * O[16 heads, 512] += P.V: warp w owns output columns 64w..64w+63 = column block w of the same
 //     tile, read with ldmatrix.x4.trans; accumulators stay in registers;
-//   * the (token, tile) sequence is cut into equal contiguous ranges, one per CTA; tokens covered by
-//     several CTAs leave partials in the workspace and are merged by the CTA that arrives last.
+//   * work split, chosen on the host: (a) a CLUSTER of 1/2/4/8 CTAs per token when that fills at
+//     least 85 % of the SMs: each CTA takes an equal share of the token's tiles and the partial
+//     results are merged through distributed shared memory (every warp's 64 output columns go to
+//     the CTA that owns that column block; no global partials, fences or atomics); (b) otherwise the
+//     (token, tile) sequence is cut into equal contiguous ranges, one per CTA, and tokens covered by
+//     several CTAs leave partials in the workspace that the last-arriving CTA merges.
+#include <cooperative_groups.h>
+
 #include <cstdlib>
 
 #include "attn_plan.cuh"
@@ -36,6 +42,8 @@
 #include "tmap.cuh"
 
 namespace dsa {
+
+namespace cg = cooperative_groups;
 
 constexpr int kMmStages = 3;
 constexpr int kMmBlockBytes = kAtTile * 128;        // 8192
@@ -49,8 +57,6 @@ struct MmShared {
   int idx[kMmStages][kAtTile];
   int live[kMmStages];
   float red[8][kHeads];
-  float merge_f[32][kHeads];
-  float merge_inv[kHeads];
   int is_last;
 };
 
@@ -81,51 +87,71 @@ __device__ __forceinline__ void cp_async_wait_group() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// Merge of the per-segment partials of one token by the 256 threads of the last-arriving CTA:
-// threads 0..15 turn the segments' (m, l) into rescale factors, then each thread owns two output
-// columns and walks the 16 heads with all loads of a segment in flight.
-__device__ void mm_merge_segments(MmShared& sh, const AtPartials& w, int t, int n_seg, int segs_max,
-                                  __nv_bfloat16* out, float* lse, int tid) {
-  if (tid < kHeads) {
-    const int h = tid;
-    float mx = -INFINITY;
-    for (int s = 0; s < n_seg; ++s) mx = fmaxf(mx, w.m[((size_t)t * segs_max + s) * kHeads + h]);
-    float lsum = 0.f;
-    for (int s = 0; s < n_seg; ++s) {
-      const size_t o = ((size_t)t * segs_max + s) * kHeads + h;
-      const float ms = w.m[o];
-      const float fs = (ms == -INFINITY) ? 0.f : exp2f(ms - mx);
-      sh.merge_f[s][h] = fs;
-      lsum += w.l[o] * fs;
+// Merge of a token's partials by the CTA that arrives last, in the accumulator layout of the
+// kernel: every thread reads, for each segment in ascending order, the 32 values it would itself
+// have written (its own segment included, so that the summation order -- and with it the result,
+// bit for bit -- does not depend on which CTA happens to arrive last).  Two segments per round
+// with all loads of a round in flight: the merge is latency-bound, one L2 round trip per round.
+__device__ __forceinline__ void mm_merge_segments(const AtPartials& part, long t, int n_seg,
+                                                  int segs_max, float (&o)[8][4],
+                                                  __nv_bfloat16* out, float* lse, int w, int g, int t4) {
+  const int col = 64 * w + 2 * t4;
+  float mx0 = -INFINITY, mx1 = -INFINITY, ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+  for (int nn = 0; nn < 8; ++nn) o[nn][0] = o[nn][1] = o[nn][2] = o[nn][3] = 0.f;
+  for (int s0 = 0; s0 < n_seg; s0 += 2) {
+    float2 v[2][16];
+    float ms[2][2], lsg[2][2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int s = s0 + u < n_seg ? s0 + u : s0;
+      const size_t slot = (size_t)t * segs_max + s;
+      const float* pa = part.acc + (slot * kHeads + g) * kCkv + col;
+#pragma unroll
+      for (int nn = 0; nn < 8; ++nn) {
+        v[u][nn] = *reinterpret_cast<const float2*>(pa + 8 * nn);
+        v[u][8 + nn] = *reinterpret_cast<const float2*>(pa + 8 * kCkv + 8 * nn);
+      }
+      ms[u][0] = part.m[slot * kHeads + g];
+      ms[u][1] = part.m[slot * kHeads + g + 8];
+      lsg[u][0] = part.l[slot * kHeads + g];
+      lsg[u][1] = part.l[slot * kHeads + g + 8];
     }
-    sh.merge_inv[h] = lsum > 0.f ? 1.f / lsum : 0.f;
-    lse[(size_t)t * kHeads + h] = lsum > 0.f ? mx + log2f(lsum) : -INFINITY;
-  }
-  __syncthreads();
-  const int c0 = tid * 2;
-  float2 a[kHeads];
 #pragma unroll
-  for (int h = 0; h < kHeads; ++h) a[h] = make_float2(0.f, 0.f);
-  for (int s = 0; s < n_seg; ++s) {
-    const float* base = w.acc + ((size_t)t * segs_max + s) * kHeads * kCkv + c0;
-    float2 v[kHeads];
+    for (int u = 0; u < 2; ++u) {
+      if (s0 + u >= n_seg) continue;
+      const float n0 = fmaxf(mx0, ms[u][0]), n1 = fmaxf(mx1, ms[u][1]);
+      const float c0 = mx0 == -INFINITY ? 0.f : exp2f(mx0 - n0), c1 = mx1 == -INFINITY ? 0.f : exp2f(mx1 - n1);
+      const float f0 = ms[u][0] == -INFINITY ? 0.f : exp2f(ms[u][0] - n0);
+      const float f1 = ms[u][1] == -INFINITY ? 0.f : exp2f(ms[u][1] - n1);
 #pragma unroll
-    for (int h = 0; h < kHeads; ++h) v[h] = *reinterpret_cast<const float2*>(base + h * kCkv);
-#pragma unroll
-    for (int h = 0; h < kHeads; ++h) {
-      const float fs = sh.merge_f[s][h];
-      a[h].x += v[h].x * fs;
-      a[h].y += v[h].y * fs;
+      for (int nn = 0; nn < 8; ++nn) {
+        o[nn][0] = o[nn][0] * c0 + v[u][nn].x * f0;
+        o[nn][1] = o[nn][1] * c0 + v[u][nn].y * f0;
+        o[nn][2] = o[nn][2] * c1 + v[u][8 + nn].x * f1;
+        o[nn][3] = o[nn][3] * c1 + v[u][8 + nn].y * f1;
+      }
+      ls0 = ls0 * c0 + lsg[u][0] * f0;
+      ls1 = ls1 * c1 + lsg[u][1] * f1;
+      mx0 = n0;
+      mx1 = n1;
     }
   }
+  const float i0 = ls0 > 0.f ? 1.f / ls0 : 0.f, i1 = ls1 > 0.f ? 1.f / ls1 : 0.f;
+  __nv_bfloat16* oa = out + ((size_t)t * kHeads + g) * kCkv + col;
+  __nv_bfloat16* ob = oa + 8 * kCkv;
 #pragma unroll
-  for (int h = 0; h < kHeads; ++h) {
-    const float inv = sh.merge_inv[h];
-    *reinterpret_cast<uint32_t*>(out + ((size_t)t * kHeads + h) * kCkv + c0) = pack_bf162(a[h].x * inv, a[h].y * inv);
+  for (int nn = 0; nn < 8; ++nn) {
+    *reinterpret_cast<uint32_t*>(oa + 8 * nn) = pack_bf162(o[nn][0] * i0, o[nn][1] * i0);
+    *reinterpret_cast<uint32_t*>(ob + 8 * nn) = pack_bf162(o[nn][2] * i1, o[nn][3] * i1);
   }
-  __syncthreads();
+  if (w == 0 && t4 == 0) {
+    lse[(size_t)t * kHeads + g] = ls0 > 0.f ? mx0 + log2f(ls0) : -INFINITY;
+    lse[(size_t)t * kHeads + g + 8] = ls1 > 0.f ? mx1 + log2f(ls1) : -INFINITY;
+  }
 }
 
+template <bool kCluster>
 __global__ void __launch_bounds__(kMmThreads, 1)
 sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloat16* __restrict__ q_pe,
                        const __nv_bfloat16* __restrict__ ckv, const __nv_bfloat16* __restrict__ kpe,
@@ -144,11 +170,19 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
   const int g = lane >> 2, t4 = lane & 3;
   const int tpt = plan.tiles_per_token;
   const long total = (long)tokens * tpt;
-  const long w0 = plan.balanced ? plan.starts[blockIdx.x] : (long)blockIdx.x * plan.per_cta;
-  const long w1 = plan.balanced ? plan.starts[blockIdx.x + 1]
-                                : (w0 + plan.per_cta < total ? w0 + plan.per_cta : total);
+  long w0, w1;
+  if (kCluster) {   // plan.per_cta holds the cluster size: rank r takes the r-th share of the token's tiles
+    const int csize = plan.per_cta, rank = (int)blockIdx.x % csize;
+    const long tok = blockIdx.x / csize;
+    w0 = tok * tpt + (long)rank * tpt / csize;
+    w1 = tok * tpt + (long)(rank + 1) * tpt / csize;
+  } else {
+    w0 = plan.balanced ? plan.starts[blockIdx.x] : (long)blockIdx.x * plan.per_cta;
+    w1 = plan.balanced ? plan.starts[blockIdx.x + 1]
+                       : (w0 + plan.per_cta < total ? w0 + plan.per_cta : total);
+  }
   const int n = (int)(w1 - w0);
-  if (n <= 0) return;
+  if (!kCluster && n <= 0) return;
   AtPartials part = at_carve(ws_raw, tokens, plan.segs_max);
 
   // ---------------- gather issue: tile `issued` goes to stage issued % 3 ------------------------
@@ -161,7 +195,7 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
     b = k1 < topk ? __ldg(indices + (size_t)tt * index_stride + k1) : -1;
   };
   ptx::grid_dependency_wait();  // the index rows may come from the kernel before us in the stream
-  load_indices(ti, ji, nv0, nv1);
+  if (n > 0) load_indices(ti, ji, nv0, nv1);
   const int sub = lane >> 3, ch = lane & 7;  // row inside a 4-row group, 16-byte chunk of a 128-byte block
   auto issue_tile = [&]() {
     if (issued < n) {
@@ -210,7 +244,7 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
     }
     cp_async_commit();
   };
-  stage_q(w0 / tpt, kv_addr + 2 * kMmStageBytes);
+  if (n > 0) stage_q(w0 / tpt, kv_addr + 2 * kMmStageBytes);
   issue_tile();
   issue_tile();
 
@@ -218,6 +252,10 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
   uint32_t qa[36][4];          // A fragments of q: k-step ks covers columns 16 ks .. 16 ks + 15
   float o[8][4];               // O[heads g / g+8][columns 64 w + 8 n + 2 t4, +1]
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  if (kCluster) {   // a rank without tiles still takes part in the merge
+#pragma unroll
+    for (int nn = 0; nn < 8; ++nn) o[nn][0] = o[nn][1] = o[nn][2] = o[nn][3] = 0.f;
+  }
   long t = w0 / tpt, cur_t = -1;
   int j = (int)(w0 - t * tpt) - 1;
 
@@ -338,7 +376,7 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
         }
       }
     }
-    if (j == tpt - 1 || i == n - 1) {
+    if (!kCluster && (j == tpt - 1 || i == n - 1)) {
       // ------------------ end of this CTA's segment of token t ------------------------------------
       float s0 = l0, s1 = l1;
       s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
@@ -394,12 +432,112 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
         __syncthreads();
         if (sh.is_last) {
           __threadfence();
-          mm_merge_segments(sh, part, (int)t, n_seg, plan.segs_max, out, lse, tid);
+          mm_merge_segments(part, t, n_seg, plan.segs_max, o, out, lse, w, g, t4);
         }
       }
     }
   }
   cp_async_wait_group<0>();
+  if (kCluster) {
+    // ---------------- merge across the token's cluster through distributed shared memory ----------
+    // Column block b (64 output columns = what warp b of every CTA holds) is merged by rank b % c:
+    // every warp sends its 16 x 64 fp32 block to that rank, every CTA sends its (m, l) to all.
+    cg::cluster_group cluster = cg::this_cluster();
+    const int csize = plan.per_cta, rank = (int)cluster.block_rank();
+    const long tok = blockIdx.x / csize;
+    float s0 = l0, s1 = l1;
+    s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+    s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+    __syncthreads();   // every warp is done with the stages and with sh.red
+    // peers write into this CTA's stage memory: they may start once every CTA of the cluster has
+    // left its tile loop (arrive here, wait just before the first remote store)
+    if (csize > 1) cluster.barrier_arrive();
+    if (t4 == 0) { sh.red[w][g] = s0; sh.red[w][g + 8] = s1; }
+    __syncthreads();
+    float lt0 = 0.f, lt1 = 0.f;
+#pragma unroll
+    for (int ww = 0; ww < 8; ++ww) { lt0 += sh.red[ww][g]; lt1 += sh.red[ww][g + 8]; }
+    const float mm0 = lt0 > 0.f ? m0 : -INFINITY, mm1 = lt1 > 0.f ? m1 : -INFINITY;
+    // exchange area at the start of the stage memory of the RECEIVING CTA:
+    //   xo[src rank][local block][16 heads][64 cols] fp32, then xml[src rank][2][16] (m, l)
+    float* xo_local = reinterpret_cast<float*>(dyn_raw + pad);
+    float* xml_local = xo_local + 8 * kHeads * 64;
+    const int dst_rank = w % csize, blk_local = w / csize, blocks_per_rank = 8 / csize;
+    if (csize > 1) {
+      cluster.barrier_wait();
+      if (dst_rank != rank) {
+        float* remote = cluster.map_shared_rank(xo_local, dst_rank) +
+                        ((size_t)(rank * blocks_per_rank + blk_local) * kHeads) * 64;
+#pragma unroll
+        for (int nn = 0; nn < 8; ++nn) {
+          *reinterpret_cast<float2*>(remote + g * 64 + 8 * nn + 2 * t4) = make_float2(o[nn][0], o[nn][1]);
+          *reinterpret_cast<float2*>(remote + (g + 8) * 64 + 8 * nn + 2 * t4) = make_float2(o[nn][2], o[nn][3]);
+        }
+      }
+      if (w == 0 && t4 == 0) {
+        for (int d = 0; d < csize; ++d) {
+          if (d == rank) continue;
+          float* r = cluster.map_shared_rank(xml_local, d) + rank * 2 * kHeads;
+          r[g] = mm0; r[g + 8] = mm1;
+          r[kHeads + g] = lt0; r[kHeads + g + 8] = lt1;
+        }
+      }
+      cluster.sync();
+    }
+    float mx0 = mm0, mx1 = mm1, ls0 = lt0, ls1 = lt1;
+    const bool merger = dst_rank == rank;
+    for (int sr = 0; sr < csize; ++sr) {
+      if (sr == rank) continue;
+      const float* ml = xml_local + sr * 2 * kHeads;
+      const float ms0 = ml[g], ms1 = ml[g + 8], lg0 = ml[kHeads + g], lg1 = ml[kHeads + g + 8];
+      const float n0 = fmaxf(mx0, ms0), n1 = fmaxf(mx1, ms1);
+      const float c0 = mx0 == -INFINITY ? 0.f : exp2f(mx0 - n0), c1 = mx1 == -INFINITY ? 0.f : exp2f(mx1 - n1);
+      const float f0 = ms0 == -INFINITY ? 0.f : exp2f(ms0 - n0), f1 = ms1 == -INFINITY ? 0.f : exp2f(ms1 - n1);
+      if (merger) {
+        const float* src = xo_local + ((size_t)(sr * blocks_per_rank + blk_local) * kHeads) * 64;
+#pragma unroll
+        for (int nn = 0; nn < 8; ++nn) {
+          const float2 va = *reinterpret_cast<const float2*>(src + g * 64 + 8 * nn + 2 * t4);
+          const float2 vb = *reinterpret_cast<const float2*>(src + (g + 8) * 64 + 8 * nn + 2 * t4);
+          o[nn][0] = o[nn][0] * c0 + va.x * f0;
+          o[nn][1] = o[nn][1] * c0 + va.y * f0;
+          o[nn][2] = o[nn][2] * c1 + vb.x * f1;
+          o[nn][3] = o[nn][3] * c1 + vb.y * f1;
+        }
+      }
+      ls0 = ls0 * c0 + lg0 * f0;
+      ls1 = ls1 * c1 + lg1 * f1;
+      mx0 = n0;
+      mx1 = n1;
+    }
+    if (merger) {
+      const float i0 = ls0 > 0.f ? 1.f / ls0 : 0.f, i1 = ls1 > 0.f ? 1.f / ls1 : 0.f;
+      const int col = 64 * w + 2 * t4;
+      __nv_bfloat16* oa = out + ((size_t)tok * kHeads + g) * kCkv + col;
+      __nv_bfloat16* ob = oa + 8 * kCkv;
+#pragma unroll
+      for (int nn = 0; nn < 8; ++nn) {
+        *reinterpret_cast<uint32_t*>(oa + 8 * nn) = pack_bf162(o[nn][0] * i0, o[nn][1] * i0);
+        *reinterpret_cast<uint32_t*>(ob + 8 * nn) = pack_bf162(o[nn][2] * i1, o[nn][3] * i1);
+      }
+    }
+    if (rank == 0 && w == 0 && t4 == 0) {
+      lse[(size_t)tok * kHeads + g] = ls0 > 0.f ? mx0 + log2f(ls0) : -INFINITY;
+      lse[(size_t)tok * kHeads + g + 8] = ls1 > 0.f ? mx1 + log2f(ls1) : -INFINITY;
+    }
+  }
+}
+
+// Cluster size for the one-cluster-per-token split, or 0 when the contiguous-range split is the
+// better fit: the largest power of two (<= 8) that keeps tokens * size within the SMs, used when it
+// fills at least 85 % of them and leaves every CTA at least four tiles.
+static int mm_cluster_size(int tokens, int tiles_per_token, int sms) {
+  int c = 1;
+  while (c < 8 && (long)tokens * c * 2 <= sms && tiles_per_token / (c * 2) >= 4) c *= 2;
+  if ((long)tokens * c > sms || (double)tokens * c < 0.85 * sms) return 0;
+  return c;
 }
 
 cudaError_t launch_sparse_attn_mma(const void* q_nope, const void* q_pe, const void* ckv,
@@ -408,31 +546,59 @@ cudaError_t launch_sparse_attn_mma(const void* q_nope, const void* q_pe, const v
                                    int64_t num_slots, void* ws, int32_t* status, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(sparse_attn_mma_kernel,
+    cudaError_t e = cudaFuncSetAttribute(sparse_attn_mma_kernel<false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmDynBytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(sparse_attn_mma_kernel<true>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmDynBytes);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  AtPlan plan = at_make_plan(tokens, topk, sm_count());
-  // The cost-balanced split was measured equal to the uniform one at the headline shape (42.3 vs
-  // 41.7 us): the slow CTAs are slow per tile, not by token starts.  DSA_ATT_BALANCED=1 enables it.
-  static int balanced = -1;
+  static double start_cost = -1.0;
+  static int balanced = -1, cluster_ok = -1;
   if (balanced < 0) {
-    const char* e = getenv("DSA_ATT_BALANCED");
+    // The cost-balanced contiguous split was measured equal to the uniform one at the headline
+    // shape (40.5-42 us for start costs 1-5 against 41.7 us).  DSA_ATT_BALANCED=1 enables it,
+    // DSA_ATT_CLUSTER=0 turns the cluster-per-token split off.
+    const char* e = getenv("DSA_ATT_START_COST");
+    start_cost = e != nullptr ? atof(e) : 1.0;
+    e = getenv("DSA_ATT_BALANCED");
     balanced = (e != nullptr && e[0] == '1') ? 1 : 0;
+    e = getenv("DSA_ATT_CLUSTER");
+    cluster_ok = (e != nullptr && e[0] == '0') ? 0 : 1;
   }
+  AtPlan plan = at_make_plan(tokens, topk, sm_count(), start_cost);
   if (!balanced) plan.balanced = 0;
+  const int csize = cluster_ok ? mm_cluster_size(tokens, plan.tiles_per_token, sm_count()) : 0;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)plan.grid);
   cfg.blockDim = dim3(kMmThreads);
   cfg.dynamicSmemBytes = kMmDynBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled();
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, sparse_attn_mma_kernel, static_cast<const __nv_bfloat16*>(q_nope),
+  if (csize > 0) {
+    plan.per_cta = csize;   // the kernel reads the cluster size from here
+    plan.balanced = 0;
+    cfg.gridDim = dim3((unsigned)(tokens * csize));
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = (unsigned)csize;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, sparse_attn_mma_kernel<true>,
+                              static_cast<const __nv_bfloat16*>(q_nope),
+                              static_cast<const __nv_bfloat16*>(q_pe),
+                              static_cast<const __nv_bfloat16*>(ckv),
+                              static_cast<const __nv_bfloat16*>(kpe), indices, index_stride,
+                              sm_scale * kMmLog2e, static_cast<__nv_bfloat16*>(out), lse, tokens, topk,
+                              num_slots, plan, ws, status);
+  }
+  cfg.gridDim = dim3((unsigned)plan.grid);
+  return cudaLaunchKernelEx(&cfg, sparse_attn_mma_kernel<false>,
+                            static_cast<const __nv_bfloat16*>(q_nope),
                             static_cast<const __nv_bfloat16*>(q_pe),
                             static_cast<const __nv_bfloat16*>(ckv),
                             static_cast<const __nv_bfloat16*>(kpe), indices, index_stride,

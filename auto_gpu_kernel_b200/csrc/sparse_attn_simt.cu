@@ -23,7 +23,7 @@ struct AttWorkspace {
 };
 
 __host__ __device__ inline size_t att_counter_bytes(int tokens) {
-  return (((size_t)tokens * 4 + 255) / 256) * 256;
+  return attn_counter_region_bytes(tokens);
 }
 
 __host__ __device__ inline AttWorkspace att_carve(void* ws, int tokens, int splits) {

@@ -62,13 +62,13 @@ def kernel(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table, topk_
     need = lib.dsa_indexer_workspace_bytes(batch, max_pages)
     ws = workspace.get(dev, "indexer", need)
     status = workspace.status_word(dev)
-    with torch.cuda.device(dev):
+    with workspace.device_guard(dev):
         rc = lib.dsa_indexer_topk(
             q_index_fp8.data_ptr(), k_index_cache_fp8.data_ptr(), weights.data_ptr(),
             seq_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0),
             topk_indices.data_ptr(), topk_indices.stride(0), batch, k_index_cache_fp8.shape[0],
             max_pages, ws.data_ptr(), ws.numel(), status.data_ptr(),
-            torch.cuda.current_stream(dev).cuda_stream)
+            workspace.stream_handle(dev))
     _lib.check(rc, "dsa_indexer_topk")
     return None
 
@@ -92,12 +92,12 @@ def scores(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table, varia
         out = torch.full((batch, width), float("nan"), dtype=torch.float32, device=q_index_fp8.device)
     lib = _lib.load()
     dev = q_index_fp8.device
-    with torch.cuda.device(dev):
+    with workspace.device_guard(dev):
         rc = lib.dsa_indexer_scores(
             q_index_fp8.data_ptr(), k_index_cache_fp8.data_ptr(), weights.data_ptr(),
             seq_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0), out.data_ptr(),
             out.stride(0), batch, k_index_cache_fp8.shape[0], max_pages, variant,
-            workspace.status_word(dev).data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+            workspace.status_word(dev).data_ptr(), workspace.stream_handle(dev))
     _lib.check(rc, "dsa_indexer_scores")
     return out
 
@@ -109,11 +109,11 @@ def select(score_rows, seq_lens, block_table, topk_indices=None):
         topk_indices = torch.empty(batch, TOPK, dtype=torch.int32, device=score_rows.device)
     lib = _lib.load()
     dev = score_rows.device
-    with torch.cuda.device(dev):
+    with workspace.device_guard(dev):
         rc = lib.dsa_topk_select(
             score_rows.data_ptr(), score_rows.stride(0), seq_lens.data_ptr(), block_table.data_ptr(),
             block_table.stride(0), topk_indices.data_ptr(), topk_indices.stride(0), batch,
             block_table.shape[1], workspace.status_word(dev).data_ptr(),
-            torch.cuda.current_stream(dev).cuda_stream)
+            workspace.stream_handle(dev))
     _lib.check(rc, "dsa_topk_select")
     return topk_indices

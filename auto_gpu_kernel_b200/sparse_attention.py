@@ -58,14 +58,14 @@ def kernel(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale, output,
     lib = _lib.load()
     need = lib.dsa_sparse_attn_workspace_bytes(tokens, HEADS, topk)
     ws = workspace.get(dev, "attention", need)
-    with torch.cuda.device(dev):
+    with workspace.device_guard(dev):
         fn = (lib.dsa_sparse_attn, lib.dsa_sparse_attn_cuda_core, lib.dsa_sparse_attn_tcgen05)[variant]
         rc = fn(
             q_nope.data_ptr(), q_pe.data_ptr(), ckv_cache.data_ptr(), kpe_cache.data_ptr(),
             sparse_indices.data_ptr(), sparse_indices.stride(0), float(sm_scale),
             output.data_ptr(), lse.data_ptr(), tokens, HEADS, topk, slots, ws.data_ptr(),
             ws.numel(), workspace.status_word(dev).data_ptr(),
-            torch.cuda.current_stream(dev).cuda_stream)
+            workspace.stream_handle(dev))
     _lib.check(rc, "dsa_sparse_attn")
     return None
 

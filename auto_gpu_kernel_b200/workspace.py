@@ -7,6 +7,8 @@ own workspace tensors instead.
 """
 from __future__ import annotations
 
+import contextlib
+
 import torch
 
 _buffers: dict = {}
@@ -31,6 +33,24 @@ def status_word(device: torch.device) -> torch.Tensor:
         word = torch.zeros(1, dtype=torch.int32, device=device)
         _status[key] = word
     return word
+
+
+_NO_GUARD = contextlib.nullcontext()
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def device_guard(device: torch.device):
+    """Context that makes `device` current for a launch; free when it already is."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(device)
+
+
+def stream_handle(device: torch.device) -> int:
+    """cudaStream_t of torch's current stream on `device` (the stream the C ABI enqueues on)."""
+    if _raw_stream is not None and device.index is not None:
+        return _raw_stream(device.index)
+    return torch.cuda.current_stream(device).cuda_stream
 
 
 STATUS_BITS = {

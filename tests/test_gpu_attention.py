@@ -41,6 +41,41 @@ def test_token_counts_against_gpu_oracle(cuda, tokens, variant):
     assert_attention_close(out, lse, ref_out.cpu(), ref_lse.cpu(), label=f"T={tokens}")
 
 
+@pytest.mark.parametrize("tokens", [16, 18, 33, 37, 63, 70, 74, 130, 148])
+def test_cluster_split_token_counts(cuda, tokens):
+    """Token counts at which the default kernel runs one cluster of 8 / 4 / 2 / 1 CTAs per token
+    and merges through distributed shared memory; rows with few valid ids leave some ranks of a
+    cluster without any live tile, and one row is fully masked."""
+    lens = wl.uniform_lengths(tokens, 40, 6000, seed=100 + tokens)
+    inp = wl.make_attention_inputs(lens, seed=100 + tokens, device=cuda)
+    idx = inp.sparse_indices.clone()
+    idx[1, 70:] = -1            # two tiles live, the rest masked
+    idx[2] = -1                 # nothing valid: output 0, lse -inf
+    idx[3, :1500] = -1          # only the last ranks see valid rows
+    inp.sparse_indices = idx
+    out, lse = sparse_attention.run(*inp.args(), variant=0)
+    workspace.check_status(cuda)
+    ref_out, ref_lse = oracle.sparse_attention(*inp.args(), output=torch.empty_like(out),
+                                               lse=torch.empty_like(lse))
+    assert_attention_close(out, lse, ref_out.cpu(), ref_lse.cpu(), label=f"cluster T={tokens}")
+    out_cc, lse_cc = sparse_attention.run(*inp.args(), variant=1)
+    assert_attention_close(out, lse, out_cc.cpu(), lse_cc.cpu(), label=f"cluster vs cuda-core T={tokens}")
+
+
+@VARIANTS
+def test_token_count_changes_between_calls(cuda, variant):
+    """One workspace serves calls of different token counts: the arrival counters of one call must
+    never sit where an earlier call with another token count left partial results."""
+    for tokens in (8, 70, 3, 130, 40, 9):
+        lens = wl.uniform_lengths(tokens, 2100, 5000, seed=7 * tokens)
+        inp = wl.make_attention_inputs(lens, seed=7 * tokens, device=cuda)
+        out, lse = sparse_attention.run(*inp.args(), variant=variant)
+        workspace.check_status(cuda)
+        ref_out, ref_lse = oracle.sparse_attention(*inp.args(), output=torch.empty_like(out),
+                                                   lse=torch.empty_like(lse))
+        assert_attention_close(out, lse, ref_out.cpu(), ref_lse.cpu(), label=f"sequence T={tokens}")
+
+
 @VARIANTS
 def test_interior_and_leading_padding(cuda, variant):
     """-1 entries anywhere in a row (not only the tail) are masked."""
