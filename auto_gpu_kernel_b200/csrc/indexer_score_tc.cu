@@ -90,27 +90,8 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   ptx::launch_dependents();  // the selection kernel may be scheduled as SMs free up; it waits for our scores
 
-  // ---- tiles per request -> exclusive prefix (all threads) ------------------------------------
-  {
-    const int chunk = (batch + kTcThreads - 1) / kTcThreads;
-    const int lo = min(batch, tid * chunk), hi = min(batch, lo + chunk);
-    int sum = 0;
-    for (int b = lo; b < hi; ++b) sum += tiles_of(seq_lens[b], max_pages, skip_short);
-    sh.partial[tid] = sum;
-    __syncthreads();
-    if (tid == 0) {
-      int run = 0;
-      for (int i = 0; i < kTcThreads; ++i) { int v = sh.partial[i]; sh.partial[i] = run; run += v; }
-      sh.prefix[batch] = run;
-      sh.abort_flag = 0;
-    }
-    __syncthreads();
-    int run = sh.partial[tid];
-    for (int b = lo; b < hi; ++b) {
-      sh.prefix[b] = run;
-      run += tiles_of(seq_lens[b], max_pages, skip_short);
-    }
-  }
+  // set-up that reads nothing from global memory, so that it can overlap the tail of the kernel
+  // before us in the stream (programmatic dependent launch)
   if (warp == 0) {
     if (lane == 0) {
       for (int i = 0; i < kTcStages; ++i) {
@@ -132,6 +113,29 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
     __syncwarp();
     ptx::tmem_alloc(smem_u32(&sh.tmem_base), kTcTmemCols);
     ptx::tmem_relinquish();
+  }
+  ptx::grid_dependency_wait();  // q, weights, seq_lens, block_table and the cache may come from it
+
+  // ---- tiles per request -> exclusive prefix (all threads) ------------------------------------
+  {
+    const int chunk = (batch + kTcThreads - 1) / kTcThreads;
+    const int lo = min(batch, tid * chunk), hi = min(batch, lo + chunk);
+    int sum = 0;
+    for (int b = lo; b < hi; ++b) sum += tiles_of(seq_lens[b], max_pages, skip_short);
+    sh.partial[tid] = sum;
+    __syncthreads();
+    if (tid == 0) {
+      int run = 0;
+      for (int i = 0; i < kTcThreads; ++i) { int v = sh.partial[i]; sh.partial[i] = run; run += v; }
+      sh.prefix[batch] = run;
+      sh.abort_flag = 0;
+    }
+    __syncthreads();
+    int run = sh.partial[tid];
+    for (int b = lo; b < hi; ++b) {
+      sh.prefix[b] = run;
+      run += tiles_of(seq_lens[b], max_pages, skip_short);
+    }
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -320,12 +324,21 @@ cudaError_t launch_indexer_score_tc(const void* q_fp8, const void* k_cache, cons
     CUtensorMap tmap_q;
     const uint8_t* qp = static_cast<const uint8_t*>(q_fp8) + (size_t)b0 * kIdxHeads * kIdxDim;
     if (!make_rows128_map(&tmap_q, qp, (uint64_t)nb * kIdxHeads)) return cudaErrorInvalidValue;
-    indexer_score_tc_kernel<<<2 * sm_count(), kTcThreads, kTcDynBytes, stream>>>(
-        tmap_k, tmap_q, static_cast<const uint8_t*>(k_cache), weights + (size_t)b0 * kIdxHeads,
-        seq_lens + b0, block_table + (size_t)b0 * bt_stride, bt_stride,
-        scores + (size_t)b0 * score_stride, score_stride, nb, num_pages, max_pages, skip_short,
-        status);
-    cudaError_t e = cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * sm_count()));
+    cfg.blockDim = dim3(kTcThreads);
+    cfg.dynamicSmemBytes = kTcDynBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled();
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(
+        &cfg, indexer_score_tc_kernel, tmap_k, tmap_q, static_cast<const uint8_t*>(k_cache),
+        weights + (size_t)b0 * kIdxHeads, seq_lens + b0, block_table + (size_t)b0 * bt_stride,
+        bt_stride, scores + (size_t)b0 * score_stride, score_stride, nb, num_pages, max_pages,
+        skip_short, status);
     if (e != cudaSuccess) return e;
   }
   return cudaSuccess;

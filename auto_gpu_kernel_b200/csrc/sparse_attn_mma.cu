@@ -169,6 +169,7 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
   const int tpt = plan.tiles_per_token;
+  ptx::launch_dependents();   // the next kernel in the stream may run its set-up under our tail
   const long total = (long)tokens * tpt;
   long w0, w1;
   if (kCluster) {   // plan.per_cta holds the cluster size: rank r takes the r-th share of the token's tiles
