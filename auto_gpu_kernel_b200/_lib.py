@@ -43,7 +43,27 @@ SIGNATURES = {
     "dsa_index_cache_write": (_c_int, [_ptr, _c_int, _c_i64, _ptr, _ptr, _c_int, _c_int, _ptr, _ptr]),
     "dsa_kv_cache_append": (_c_int, [_ptr, _c_i64, _ptr, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64,
                                      _ptr, _ptr]),
+    "dsa_decode_step_host": (_c_int, [_ptr]),
 }
+
+
+class HostStepArgs(ctypes.Structure):
+    """Mirror of `dsa_host_step_args` in include/dsa_b200.h (same order, same types)."""
+    _fields_ = [
+        ("host_in", _ptr), ("dev_in", _ptr), ("in_indexer_bytes", _c_size),
+        ("in_attention_bytes", _c_size), ("host_out", _ptr), ("dev_out", _ptr),
+        ("out_attention_bytes", _c_size), ("out_indices_bytes", _c_size),
+        ("q_index_fp8", _ptr), ("weights", _ptr), ("seq_lens", _ptr), ("block_table", _ptr),
+        ("block_table_stride", _c_i64), ("q_nope", _ptr), ("q_pe", _ptr), ("output", _ptr),
+        ("lse", _ptr), ("topk_indices", _ptr),
+        ("k_index_cache", _ptr), ("ckv_cache", _ptr), ("kpe_cache", _ptr),
+        ("batch", _c_int), ("num_pages", _c_int), ("max_pages", _c_int), ("num_slots", _c_i64),
+        ("sm_scale", _c_float), ("indexer_workspace", _ptr), ("indexer_workspace_bytes", _c_size),
+        ("attention_workspace", _ptr), ("attention_workspace_bytes", _c_size),
+        ("status_dev", _ptr), ("stream", _ptr), ("side_stream", _ptr),
+        ("ev_first_copy", _ptr), ("ev_q_ready", _ptr), ("ev_indices_ready", _ptr),
+    ]
+
 
 _lib = None
 

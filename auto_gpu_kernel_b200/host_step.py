@@ -9,10 +9,11 @@ device mirror of each and a side stream, and runs
                   attention  ->  D2H [output | lse]
     side stream : H2D [q_nope | q_pe]  (under the indexer)   ...   D2H indices (under the attention)
 
-so that a step costs two copies on the critical path instead of nine.  The paged caches are
-device-resident state, as for the reference's callers.  The caller fills `inputs.*` in place (or
-passes tensors to `run`, which copies them into the slab first) and reads `outputs.*` after `run`
-returns; `run` synchronises.
+so that a step costs two copies on the critical path instead of nine.  The whole sequence is one
+call of the C ABI (`dsa_decode_step_host`): the Python side only fills a struct once.  The paged
+caches are device-resident state, as for the reference's callers.  The caller fills `inputs.*` in
+place (or passes tensors to `run`, which copies them into the slab first) and reads `outputs.*`
+after `run` returns; `run` synchronises.
 """
 from __future__ import annotations
 
@@ -21,7 +22,9 @@ from types import SimpleNamespace
 
 import torch
 
-from . import indexer, sparse_attention
+import ctypes
+
+from . import _lib, indexer, workspace
 
 ALIGN = 256
 
@@ -102,11 +105,40 @@ class HostDecodeStep:
             setattr(self._d, k, v)
         self._r = _views(self._dev_out, fr)
         self._side = torch.cuda.Stream(self.device)
-        self._q_ready = torch.cuda.Event()
-        self._idx_ready = torch.cuda.Event()
-        self._a_done = torch.cuda.Event()
         self.h2d_bytes = sum(f.nbytes for f in fa) + sum(f.nbytes for f in fb)
         self.d2h_bytes = sum(f.nbytes for f in fr)
+        # workspaces of its own: the shared grow-only ones may move when another call grows them
+        lib = _lib.load()
+        with torch.cuda.device(self.device):
+            iws = lib.dsa_indexer_workspace_bytes(batch, max_pages)
+            aws = lib.dsa_sparse_attn_workspace_bytes(batch, heads, indexer.TOPK)
+            self._iws = torch.zeros(iws, dtype=torch.uint8, device=self.device)
+            self._aws = torch.zeros(aws, dtype=torch.uint8, device=self.device)
+            self._events = [torch.cuda.Event() for _ in range(3)]
+            for ev in self._events:      # an event gets its handle when it is first recorded
+                ev.record(self._side)
+            self._side.synchronize()
+        d, r = self._d, self._r
+        self._args = _lib.HostStepArgs(
+            host_in=self._host_in.data_ptr(), dev_in=self._dev_in.data_ptr(),
+            in_indexer_bytes=na, in_attention_bytes=nb,
+            host_out=self._host_out.data_ptr(), dev_out=self._dev_out.data_ptr(),
+            out_attention_bytes=self._split, out_indices_bytes=nr - self._split,
+            q_index_fp8=d.q_index_fp8.data_ptr(), weights=d.weights.data_ptr(),
+            seq_lens=d.seq_lens.data_ptr(), block_table=d.block_table.data_ptr(),
+            block_table_stride=max_pages, q_nope=d.q_nope.data_ptr(), q_pe=d.q_pe.data_ptr(),
+            output=r.output.data_ptr(), lse=r.lse.data_ptr(), topk_indices=r.topk_indices.data_ptr(),
+            k_index_cache=k_index_cache_fp8.data_ptr(), ckv_cache=ckv_cache.data_ptr(),
+            kpe_cache=kpe_cache.data_ptr(), batch=batch, num_pages=k_index_cache_fp8.shape[0],
+            max_pages=max_pages, num_slots=ckv_cache.numel() // 512, sm_scale=sm_scale,
+            indexer_workspace=self._iws.data_ptr(), indexer_workspace_bytes=iws,
+            attention_workspace=self._aws.data_ptr(), attention_workspace_bytes=aws,
+            status_dev=workspace.status_word(self.device).data_ptr(),
+            stream=0, side_stream=self._side.cuda_stream,
+            ev_first_copy=self._events[0].cuda_event, ev_q_ready=self._events[1].cuda_event,
+            ev_indices_ready=self._events[2].cuda_event)
+        self._args_ref = ctypes.byref(self._args)
+        self._lib = lib
 
     def run(self, q_index_fp8=None, weights=None, seq_lens=None, block_table=None, q_nope=None,
             q_pe=None):
@@ -119,26 +151,8 @@ class HostDecodeStep:
                 dst = getattr(self.inputs, name)
                 dst.copy_(t.view(torch.uint8) if name == "q_index_fp8" and t.element_size() == 1
                           and t.dtype != torch.uint8 else t)
-        na, nb = self._na, self._nb
-        main = torch.cuda.current_stream(self.device)
-        side = self._side
-        self._dev_in[:na].copy_(self._host_in[:na], non_blocking=True)
-        self._a_done.record(main)
-        with torch.cuda.stream(side):
-            side.wait_event(self._a_done)   # one H2D copy at a time: the indexer's inputs go first
-            self._dev_in[na:na + nb].copy_(self._host_in[na:na + nb], non_blocking=True)
-            self._q_ready.record(side)
-        d, r = self._d, self._r
-        indexer.kernel(d.q_index_fp8.view(torch.float8_e4m3fn), self.k_index_cache_fp8, d.weights,
-                       d.seq_lens, d.block_table, r.topk_indices)
-        self._idx_ready.record(main)
-        main.wait_event(self._q_ready)
-        sparse_attention.kernel(d.q_nope, d.q_pe, self.ckv_cache, self.kpe_cache, r.topk_indices,
-                                self.sm_scale, r.output, r.lse)
-        with torch.cuda.stream(side):
-            side.wait_event(self._idx_ready)
-            self._host_out[self._split:].copy_(self._dev_out[self._split:], non_blocking=True)
-        self._host_out[:self._split].copy_(self._dev_out[:self._split], non_blocking=True)
-        side.synchronize()
-        main.synchronize()
+        self._args.stream = workspace.stream_handle(self.device)
+        with workspace.device_guard(self.device):
+            rc = self._lib.dsa_decode_step_host(self._args_ref)
+        _lib.check(rc, "dsa_decode_step_host")
         return self.outputs.topk_indices, self.outputs.output, self.outputs.lse

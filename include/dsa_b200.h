@@ -185,6 +185,60 @@ int dsa_kv_cache_append(const void* ckv, int64_t ckv_stride, const void* kpe, in
                         const int32_t* slots, void* ckv_cache, void* kpe_cache, int tokens,
                         int64_t num_slots, int32_t* status_dev, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * One decode step with HOST buffers: copies in, dsa_indexer_topk, dsa_sparse_attn over the
+ * indexer's own indices, copies out, synchronised on return.  No counterpart in the reference,
+ * whose callers pass CUDA tensors (kbench/flashinfer.py:109-120); it replaces the nine copies and
+ * two operator calls such a caller would issue itself.
+ *
+ * host_in / dev_in : one pinned slab and its device mirror,
+ *     [ indexer inputs: in_indexer_bytes ][ attention inputs: in_attention_bytes ];
+ *     q_index_fp8, weights, seq_lens, block_table point into the first part of dev_in, q_nope and
+ *     q_pe into the second (any 16-byte aligned packing).
+ * host_out / dev_out : [ output | lse : out_attention_bytes ][ topk_indices : out_indices_bytes ];
+ *     output, lse and topk_indices point into dev_out accordingly (topk rows dense, stride 2048).
+ * Caches, workspaces and status word as for the two operator calls.  `stream` carries the kernels,
+ * `side_stream` the overlapped copies; the three events are the caller's (created once, reused).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct dsa_host_step_args {
+  const void* host_in;
+  void* dev_in;
+  size_t in_indexer_bytes, in_attention_bytes;
+  void* host_out;
+  const void* dev_out;
+  size_t out_attention_bytes, out_indices_bytes;
+  /* device views into dev_in / dev_out */
+  const void* q_index_fp8;
+  const float* weights;
+  const int32_t* seq_lens;
+  const int32_t* block_table;
+  int64_t block_table_stride;
+  const void* q_nope;
+  const void* q_pe;
+  void* output;
+  float* lse;
+  int32_t* topk_indices;
+  /* device-resident state */
+  const void* k_index_cache;
+  const void* ckv_cache;
+  const void* kpe_cache;
+  int batch, num_pages, max_pages;
+  int64_t num_slots;
+  float sm_scale;
+  void* indexer_workspace;
+  size_t indexer_workspace_bytes;
+  void* attention_workspace;
+  size_t attention_workspace_bytes;
+  int32_t* status_dev;
+  void* stream;
+  void* side_stream;
+  void* ev_first_copy;
+  void* ev_q_ready;
+  void* ev_indices_ready;
+} dsa_host_step_args;
+
+int dsa_decode_step_host(const dsa_host_step_args* args);
+
 #ifdef __cplusplus
 }
 #endif
