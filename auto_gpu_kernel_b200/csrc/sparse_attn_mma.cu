@@ -532,11 +532,13 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
 }
 
 // Cluster size for the one-cluster-per-token split, or 0 when the contiguous-range split is the
-// better fit.  The largest power of two (<= 8) that keeps tokens * size within the SMs and leaves
-// every CTA at least four tiles is used (a) when it fills at least 85 % of the SMs, or (b) when 8
-// CTAs per token fit in one wave (15 such clusters on a B200): the contiguous split would cut such
-// a token into 10-148 segments and pay one L2 round trip per pair of segments in the merge
-// (measured per call at 12 tokens: 16.7 us against 20.6 us; at 1 token 16 us against 29 us).
+// better fit.  Candidates are the largest power of two (<= 8) that keeps tokens * size within the
+// SMs, leaves every CTA at least four tiles and fits in ONE wave of clusters.  The choice follows
+// a cost model fitted to per-call times at 12-120 tokens x 2048 rows (microseconds after the
+// common start-up): cluster = 1.65 * tiles per CTA; contiguous = 1.86 * tiles per SM + 8, the 8
+// being the partial flush, the q re-staging at token boundaries and the L2 round trips of the
+// last-arriver merge.  An 8-CTA cluster always wins where it fits (16.7 against 20.6 us at 12
+// tokens, 16 against 29 us at one).
 // Clusters of `csize` CTAs of this kernel that can be resident at once (a cluster needs all its
 // SMs inside one GPC, so this is less than SMs / csize for the larger sizes); queried once.
 static int mm_max_active_clusters(int csize) {
@@ -568,8 +570,10 @@ static int mm_cluster_size(int tokens, int tiles_per_token, int sms) {
   while (c < 8 && (long)tokens * c * 2 <= sms && tiles_per_token / (c * 2) >= 4) c *= 2;
   while (c > 1 && tokens > mm_max_active_clusters(c)) c /= 2;   // one wave of clusters only
   if ((long)tokens * c > sms) return 0;
-  if (c == 8 || (double)tokens * c >= 0.85 * sms) return c;
-  return 0;
+  if (c == 8) return c;
+  const double est_cluster = 1.65 * (double)((tiles_per_token + c - 1) / c);
+  const double est_contiguous = 1.86 * (double)tokens * tiles_per_token / sms + 8.0;
+  return est_cluster <= est_contiguous ? c : 0;
 }
 
 cudaError_t launch_sparse_attn_mma(const void* q_nope, const void* q_pe, const void* ckv,
