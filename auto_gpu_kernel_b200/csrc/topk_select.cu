@@ -4,14 +4,16 @@
 // One thread-block CLUSTER of 1, 2 or 4 CTAs (1024 threads each) per request: the row is cut into
 // equal segments, one per CTA, so that a small batch still uses every SM; the CTAs exchange only
 // their min/max, their 2048-bin histograms, their counts and the few boundary candidates through
-// distributed shared memory.  A segment is staged in shared memory when it fits (<= 49152 scores),
+// distributed shared memory.  A segment is staged in shared memory when it fits (<= 45056 scores),
 // otherwise every sweep streams it from L2/global.
 //
 // Fast path (three sweeps): (A) min and max of the row; (B) a 2048-bin histogram over the LINEAR
 // map of [min,max] -- scores of one request are spread over hundreds of bins, so shared-memory
 // atomics rarely collide, unlike a histogram of the leading float bits where a few exponent bins
-// take everything; (C) every element in a bin above the boundary bin is emitted (warp-aggregated
-// slot allocation), the few elements inside the boundary bin become candidates.  The linear map
+// take everything, and the staged scores are replaced in place by their bins; (C) one sweep over the
+// bins: an element of a bin above the boundary bin is emitted at (elements in higher bins) + (its
+// rank inside the bin, from a per-bin cursor), the few elements inside the boundary bin become
+// candidates.  The linear map
 // is monotone, so the bins order the elements exactly; the candidates are then ranked exactly by
 // (order-preserving 32-bit key, lower position first) and the missing number of them is emitted.
 // Fallback: when the boundary bin holds more than 1024 elements (flat or degenerate rows, massive
@@ -29,7 +31,7 @@ namespace dsa {
 namespace cg = cooperative_groups;
 
 constexpr int kSelThreads = 1024;
-constexpr int kSelRowCap = 49152;  // scores staged in dynamic shared memory (192 KB)
+constexpr int kSelRowCap = 45056;  // scores staged in dynamic shared memory (176 KB + 41 KB static)
 constexpr int kSelBins = 2048;
 constexpr int kSelCandCap = 1024;
 constexpr int kSelTableCap = 2048;      // block_table entries staged in shared memory (128K tokens)
@@ -42,9 +44,10 @@ struct SelShared {
   int32_t table[kSelTableCap];
   uint32_t warp_sums[32];
   uint32_t red_a[32], red_b[32];
-  uint32_t digit, above, ties, cnt_gt, cnt_gt2, cnt_eq, cnt_cand, kmin, kmax;
-  uint32_t tot[kSelBins];          // histogram summed over the cluster
-  uint32_t peer_min[4], peer_max[4], peer_gt[4], peer_cand[4];  // written by the peers
+  uint32_t digit, above, ties, cnt_gt2, cnt_eq, cnt_cand, kmin, kmax;
+  uint32_t tot[kSelBins];          // histogram summed over the cluster, then: elements in higher bins
+  uint32_t low[kSelBins];          // this bin's elements in lower-ranked CTAs, then: output cursor
+  uint32_t peer_min[4], peer_max[4], peer_cand[4];  // written by the peers
 };
 
 // Inclusive prefix sum over the CTA in thread order.
@@ -74,14 +77,19 @@ __device__ __forceinline__ uint32_t block_inclusive_scan(uint32_t v, uint32_t* w
 
 // Find the digit d (bins are scanned from the top) such that count(bins > d) < k <= count(bins >= d).
 // Thread t owns bins nb-1-per*t ... downwards.  Results in sh.digit / sh.above / sh.ties.
-__device__ __forceinline__ void find_boundary_bin(SelShared& sh, const uint32_t* hist, uint32_t nb,
-                                                  uint32_t k) {
+// With `to_above`, hist[bin] is replaced by the number of elements in higher bins.
+__device__ __forceinline__ void find_boundary_bin(SelShared& sh, uint32_t* hist, uint32_t nb,
+                                                  uint32_t k, bool to_above = false) {
   const int tid = threadIdx.x;
   const int per = nb / kSelThreads;  // 2 or 1
   uint32_t c_hi = hist[nb - 1 - per * tid];
   uint32_t c_lo = per == 2 ? hist[nb - 2 - per * tid] : 0u;
   uint32_t incl = block_inclusive_scan(c_hi + c_lo, sh.warp_sums);
   uint32_t excl = incl - (c_hi + c_lo);
+  if (to_above) {
+    hist[nb - 1 - per * tid] = excl;
+    if (per == 2) hist[nb - 2 - per * tid] = excl + c_hi;
+  }
   if (excl < k && k <= incl) {
     if (excl + c_hi >= k) {
       sh.digit = nb - 1 - per * tid; sh.above = excl; sh.ties = c_hi;
@@ -163,7 +171,7 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
     }
     if (lane == 0) { sh.red_a[warp] = __float_as_uint(mn); sh.red_b[warp] = __float_as_uint(mx); }
     for (int i = tid; i < kSelBins; i += kSelThreads) sh.hist[i] = 0;
-    if (tid == 0) { sh.cnt_gt = 0; sh.cnt_gt2 = 0; sh.cnt_eq = 0; sh.cnt_cand = 0; }
+    if (tid == 0) { sh.cnt_gt2 = 0; sh.cnt_eq = 0; sh.cnt_cand = 0; }
     __syncthreads();
     if (warp == 0) {
       mn = __uint_as_float(sh.red_a[lane]);
@@ -197,51 +205,76 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   };
 
   // ---- sweep B: histogram of the linear bins, summed over the cluster ---------------------------
-  for (int i = seg_lo + tid; i < seg_hi; i += kSelThreads) atomicAdd(&sh.hist[bin_of(value_at(i))], 1u);
+  // A staged score is replaced in place by its bin: the last sweep needs nothing else (the few
+  // boundary-bin elements re-read their score from L2).
+  int* bin_s = reinterpret_cast<int*>(row_s);
+  // four elements per thread and step: the loads, the bin arithmetic and the atomics of the four
+  // are independent, which hides the shared-memory latency that a one-element loop exposes
+  const int n4s = staged ? (seg_len & ~3) : 0;
+  for (int i = tid * 4; i < n4s; i += kSelThreads * 4) {
+    const float4 q = *reinterpret_cast<const float4*>(row_s + i);
+    const int4 bq = make_int4(bin_of(q.x), bin_of(q.y), bin_of(q.z), bin_of(q.w));
+    *reinterpret_cast<int4*>(bin_s + i) = bq;
+    atomicAdd(&sh.hist[bq.x], 1u);
+    atomicAdd(&sh.hist[bq.y], 1u);
+    atomicAdd(&sh.hist[bq.z], 1u);
+    atomicAdd(&sh.hist[bq.w], 1u);
+  }
+  for (int i = seg_lo + n4s + tid; i < seg_hi; i += kSelThreads) {
+    const int bin = bin_of(value_at(i));
+    if (staged) bin_s[i - seg_lo] = bin;
+    atomicAdd(&sh.hist[bin], 1u);
+  }
   cluster.sync();
   for (int k = tid; k < kSelBins; k += kSelThreads) {
-    uint32_t c = 0;
-    for (int r = 0; r < csize; ++r) c += cluster.map_shared_rank(&sh, r)->hist[k];
+    uint32_t c = 0, below_me = 0;
+    for (int r = 0; r < csize; ++r) {
+      const uint32_t h = cluster.map_shared_rank(&sh, r)->hist[k];
+      c += h;
+      if (r < crank) below_me += h;
+    }
     sh.tot[k] = c;
+    sh.low[k] = below_me;
   }
   __syncthreads();
-  find_boundary_bin(sh, sh.tot, kSelBins, kTopK);   // every CTA finds the same boundary
+  find_boundary_bin(sh, sh.tot, kSelBins, kTopK, true);   // every CTA finds the same boundary
   const int edge = (int)sh.digit;          // boundary bin
   const uint32_t above = sh.above;         // elements in higher bins: all selected
   const uint32_t in_edge = sh.ties;        // elements in the boundary bin (whole row)
   const uint32_t need = kTopK - above;     // how many of them are selected (>= 1)
   const bool few = in_edge <= (uint32_t)kSelCandCap;
-  __syncthreads();
 
-  // ---- sweep C: count, agree on output offsets, emit; collect the boundary bin ------------------
-  uint32_t mine = 0;
-  for (int i = seg_lo + tid; i < seg_hi; i += kSelThreads) mine += bin_of(value_at(i)) > edge ? 1u : 0u;
-  uint32_t incl = mine;
+  // ---- sweep C: emit; collect the boundary bin --------------------------------------------------
+  // An element of bin k > edge goes to tot[k] (elements in higher bins, whole row) + its rank
+  // inside the bin: first the lower-ranked CTAs' share (low[k]), then this CTA's in arrival order.
+  auto candidate = [&](int i) {
+    const uint32_t c = atomicAdd(&sh.cnt_cand, 1u);
+    if (c < (uint32_t)kSelCandCap) { sh.cand_key[c] = float_to_ordered(__ldg(row + i)); sh.cand_idx[c] = i; }
+  };
+  for (int i = tid * 4; i < n4s; i += kSelThreads * 4) {
+    const int4 bq = *reinterpret_cast<const int4*>(bin_s + i);
+    const int bins[4] = {bq.x, bq.y, bq.z, bq.w};
+    uint32_t rank_in_bin[4];
 #pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const uint32_t n = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += n;
-  }
-  uint32_t wbase = 0;
-  if (lane == 31) wbase = atomicAdd(&sh.cnt_gt, incl);
-  wbase = __shfl_sync(0xffffffffu, wbase, 31);
-  __syncthreads();
-  if (tid < csize) cluster.map_shared_rank(&sh, tid)->peer_gt[crank] = sh.cnt_gt;
-  cluster.sync();
-  uint32_t cta_base = 0;
-  for (int r = 0; r < crank; ++r) cta_base += sh.peer_gt[r];
-  {
-    uint32_t pos = cta_base + wbase + incl - mine;
-    for (int i = seg_lo + tid; i < seg_hi; i += kSelThreads) {
-      const float v = value_at(i);
-      const int bin = bin_of(v);
-      if (bin > edge) {
-        if (pos < (uint32_t)kTopK) out_row[pos] = slot_of(i);
-        ++pos;
-      } else if (few && bin == edge) {
-        const uint32_t c = atomicAdd(&sh.cnt_cand, 1u);
-        if (c < (uint32_t)kSelCandCap) { sh.cand_key[c] = float_to_ordered(v); sh.cand_idx[c] = i; }
+    for (int e = 0; e < 4; ++e)   // the four cursor updates are in flight together
+      rank_in_bin[e] = bins[e] > edge ? atomicAdd(&sh.low[bins[e]], 1u) : 0u;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (bins[e] > edge) {
+        const uint32_t pos = sh.tot[bins[e]] + rank_in_bin[e];
+        if (pos < (uint32_t)kTopK) out_row[pos] = slot_of(seg_lo + i + e);
+      } else if (few && bins[e] == edge) {
+        candidate(seg_lo + i + e);
       }
+    }
+  }
+  for (int i = seg_lo + n4s + tid; i < seg_hi; i += kSelThreads) {
+    const int bin = staged ? bin_s[i - seg_lo] : bin_of(__ldg(row + i));
+    if (bin > edge) {
+      const uint32_t pos = sh.tot[bin] + atomicAdd(&sh.low[bin], 1u);
+      if (pos < (uint32_t)kTopK) out_row[pos] = slot_of(i);
+    } else if (few && bin == edge) {
+      candidate(i);
     }
   }
   __syncthreads();
@@ -252,7 +285,7 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
     // ---- exact ranking of the candidates by the first CTA: higher key first, lower position
     //      first on ties ------------------------------------------------------------------------
     if (crank == 0) {
-      uint32_t n = min(sh.peer_cand[0], (uint32_t)kSelCandCap), gt_total = sh.peer_gt[0];
+      uint32_t n = min(sh.peer_cand[0], (uint32_t)kSelCandCap);
       for (int r = 1; r < csize; ++r) {
         const uint32_t nr = min(sh.peer_cand[r], (uint32_t)kSelCandCap - n);
         const SelShared* peer = cluster.map_shared_rank(&sh, r);
@@ -261,7 +294,6 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
           sh.cand_idx[n + j] = peer->cand_idx[j];
         }
         n += nr;
-        gt_total += sh.peer_gt[r];
       }
       __syncthreads();
       if (tid < (int)n) {
@@ -278,7 +310,7 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
         }
         if (rank < need) out_row[above + rank] = slot_of(ia);
       }
-      if (tid == 0 && (gt_total != above || n != in_edge)) raise_status(status, DSA_STATUS_TOPK_COUNT);
+      if (tid == 0 && n != in_edge) raise_status(status, DSA_STATUS_TOPK_COUNT);
     }
     cluster.sync();  // the peers' shared memory stays alive until the first CTA has read it
     return;
@@ -353,9 +385,7 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
       }
     }
     __syncthreads();
-    uint32_t gt_total = 0;
-    for (int r = 0; r < csize; ++r) gt_total += sh.peer_gt[r];
-    if (tid == 0 && (gt_total != above || sh.cnt_gt2 != n_gt)) raise_status(status, DSA_STATUS_TOPK_COUNT);
+    if (tid == 0 && sh.cnt_gt2 != n_gt) raise_status(status, DSA_STATUS_TOPK_COUNT);
   }
   cluster.sync();
 }

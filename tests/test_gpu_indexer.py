@@ -64,10 +64,10 @@ def _check_selection(row, n, table_row, got_row):
     assert torch.equal(torch.sort(row[local], descending=True).values, want)
 
 
-@pytest.mark.parametrize("length", [2049, 5000, 49152, 49153, 131072])
+@pytest.mark.parametrize("length", [2049, 5000, 5003, 45056, 45057, 49153, 131072])
 def test_select_against_torch_topk(cuda, length):
     """Selection alone on synthetic rows: positive, negative and mixed scores; staged and streamed
-    row paths (the boundary is 49152 scores)."""
+    row paths (the boundary is 45056 scores), lengths that are not multiples of four."""
     gen = torch.Generator(device="cpu").manual_seed(length)
     pages = (length + 63) // 64
     table = torch.randperm(pages, generator=gen).to(torch.int32).unsqueeze(0).repeat(3, 1)
