@@ -10,9 +10,9 @@ cudaError_t launch_indexer_score_simt(const void*, const void*, const float*, co
                                       int32_t*, cudaStream_t);
 cudaError_t launch_indexer_score_tc(const void*, const void*, const float*, const int32_t*,
                                     const int32_t*, int64_t, float*, int64_t, int, int, int, int,
-                                    int32_t*, cudaStream_t);
+                                    uint32_t*, int32_t*, cudaStream_t);
 cudaError_t launch_topk_select(const float*, int64_t, const int32_t*, const int32_t*, int64_t,
-                               int32_t*, int64_t, int, int, int32_t*, cudaStream_t);
+                               int32_t*, int64_t, int, int, uint32_t*, int32_t*, cudaStream_t);
 cudaError_t launch_sparse_attn_simt(const void*, const void*, const void*, const void*,
                                     const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
                                     int, void*, int32_t*, cudaStream_t);
@@ -62,15 +62,19 @@ const char* dsa_b200_error_string(int code) {
   return "dsa_b200: unknown error code";
 }
 
+// [ per request: max of the ordered score keys, max of their complements | fp32 score rows ]
+// The min / max words must be zero between calls (the selection puts them back), so their region
+// has one fixed size for every shape: no call's score rows ever land on another call's words.
+constexpr size_t kMinmaxRegionBytes = 65536 * 2 * sizeof(uint32_t);   // batch <= 65535
 size_t dsa_indexer_workspace_bytes(int batch, int max_pages) {
   if (batch <= 0 || max_pages <= 0) return 256;
-  return round256((size_t)batch * score_row_stride(max_pages) * sizeof(float));
+  return kMinmaxRegionBytes + round256((size_t)batch * score_row_stride(max_pages) * sizeof(float));
 }
 
 static int scores_impl(const void* q_fp8, const void* k_cache, const float* weights,
                        const int32_t* seq_lens, const int32_t* block_table,
                        int64_t block_table_stride, float* scores, int64_t score_stride, int batch,
-                       int num_pages, int max_pages, int variant, int skip_short,
+                       int num_pages, int max_pages, int variant, int skip_short, uint32_t* minmax,
                        int32_t* status_dev, void* stream) {
   if (batch == 0) return DSA_OK;
   if (!q_fp8 || !k_cache || !weights || !seq_lens || !block_table || !scores)
@@ -94,7 +98,7 @@ static int scores_impl(const void* q_fp8, const void* k_cache, const float* weig
   } else if (variant == 0 || variant == 2) {
     e = dsa::launch_indexer_score_tc(q_fp8, k_cache, weights, seq_lens, block_table,
                                      block_table_stride, scores, score_stride, batch, num_pages,
-                                     max_pages, skip_short, status_dev, s);
+                                     max_pages, skip_short, minmax, status_dev, s);
   } else {
     return DSA_ERR_UNSUPPORTED;
   }
@@ -107,7 +111,7 @@ int dsa_indexer_scores(const void* q_fp8, const void* k_cache, const float* weig
                        int num_pages, int max_pages, int variant, int32_t* status_dev,
                        void* stream) {
   return scores_impl(q_fp8, k_cache, weights, seq_lens, block_table, block_table_stride, scores,
-                     score_stride, batch, num_pages, max_pages, variant, 0, status_dev, stream);
+                     score_stride, batch, num_pages, max_pages, variant, 0, nullptr, status_dev, stream);
 }
 
 int dsa_topk_select(const float* scores, int64_t score_stride, const int32_t* seq_lens,
@@ -120,7 +124,7 @@ int dsa_topk_select(const float* scores, int64_t score_stride, const int32_t* se
     return DSA_ERR_BAD_SHAPE;
   return static_cast<int>(dsa::launch_topk_select(scores, score_stride, seq_lens, block_table,
                                                   block_table_stride, topk_out, topk_stride, batch,
-                                                  max_pages, status_dev,
+                                                  max_pages, nullptr, status_dev,
                                                   static_cast<cudaStream_t>(stream)));
 }
 
@@ -134,14 +138,29 @@ int dsa_indexer_topk(const void* q_fp8, const void* k_cache, const float* weight
   if (workspace_bytes < dsa_indexer_workspace_bytes(batch, max_pages))
     return DSA_ERR_WORKSPACE_TOO_SMALL;
   if (reinterpret_cast<uintptr_t>(workspace) & 255u) return DSA_ERR_MISALIGNED;
-  float* scores = static_cast<float*>(workspace);
+  if (batch > 65535) return DSA_ERR_BAD_SHAPE;
+  float* scores = reinterpret_cast<float*>(static_cast<char*>(workspace) + kMinmaxRegionBytes);
   const int64_t stride = score_row_stride(max_pages);
-  // rows of at most 2048 tokens are emitted whole by the selection: their scores are skipped
-  int rc = scores_impl(q_fp8, k_cache, weights, seq_lens, block_table, block_table_stride, scores,
-                       stride, batch, num_pages, max_pages, 0, 1, status_dev, stream);
-  if (rc != DSA_OK) return rc;
-  return dsa_topk_select(scores, stride, seq_lens, block_table, block_table_stride, topk_out,
-                         topk_stride, batch, max_pages, status_dev, stream);
+  // The streaming scorer leaves every row's min / max in front of the score rows (the words start
+  // at zero and the selection puts them back to zero); the shared-pages scorer does not.
+  const bool shared_pages = block_table_stride == 0 && batch >= dsa::kPrefillMinRows;
+  uint32_t* minmax = shared_pages ? nullptr : static_cast<uint32_t*>(workspace);
+  // rows of at most 2048 tokens are emitted whole by the selection: their scores are skipped, and
+  // when no row can be longer (max_pages <= 32) the scorer is not launched at all (the reference's
+  // GPU dispatch takes the same shortcut from the shape alone, indexer_fused.py:358-380)
+  if ((int64_t)max_pages * dsa::kPage > dsa::kTopK) {
+    int rc = scores_impl(q_fp8, k_cache, weights, seq_lens, block_table, block_table_stride, scores,
+                         stride, batch, num_pages, max_pages, 0, 1, minmax, status_dev, stream);
+    if (rc != DSA_OK) return rc;
+  } else if (!q_fp8 || !k_cache || !weights || !seq_lens || !block_table) {
+    return DSA_ERR_NULL_POINTER;
+  }
+  if (!seq_lens || !block_table || !topk_out) return DSA_ERR_NULL_POINTER;
+  if (max_pages <= 0 || topk_stride < dsa::kTopK || block_table_stride < 0) return DSA_ERR_BAD_SHAPE;
+  return static_cast<int>(dsa::launch_topk_select(scores, stride, seq_lens, block_table,
+                                                  block_table_stride, topk_out, topk_stride, batch,
+                                                  max_pages, minmax, status_dev,
+                                                  static_cast<cudaStream_t>(stream)));
 }
 
 size_t dsa_sparse_attn_workspace_bytes(int tokens, int heads, int topk) {

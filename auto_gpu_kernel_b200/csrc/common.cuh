@@ -49,6 +49,13 @@ __host__ __device__ inline size_t attn_counter_region_bytes(int tokens) {
   return need < 16384 ? 16384 : need;
 }
 
+__device__ __forceinline__ float ordered_to_float(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
+}
+
+// -inf and NaN scores are ranked as this value by the selection (and by the scorer's min / max).
+constexpr float kScoreFloor = -3.0e38f;
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -143,16 +143,29 @@ indexer_score_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k,
     const int lo = min(groups, tid * chunk), hi = min(groups, lo + chunk);
     int sum = 0;
     for (int g = lo; g < hi; ++g) sum += group_tiles(seq_lens, g, rows, max_pages, skip_short);
-    sh.partial[tid] = sum;
+    // exclusive scan of the per-thread sums: inside each warp by shuffles, then over the warps
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    if (lane == 31) sh.partial[warp] = incl;
     __syncthreads();
-    if (tid == 0) {
-      int run = 0;
-      for (int i = 0; i < kPfThreads; ++i) { int v = sh.partial[i]; sh.partial[i] = run; run += v; }
-      sh.prefix[groups] = run;
-      sh.abort_flag = 0;
+    if (warp == 0) {
+      const int nw = kPfThreads / 32;
+      int wsum = lane < nw ? sh.partial[lane] : 0, wincl = wsum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, wincl, o);
+        if (lane >= o) wincl += up;
+      }
+      if (lane < nw) sh.partial[lane] = wincl - wsum;   // tiles before this warp
+      if (lane == nw - 1) sh.prefix[groups] = wincl;
+      if (lane == 0) sh.abort_flag = 0;
     }
     __syncthreads();
-    int run = sh.partial[tid];
+    int run = sh.partial[warp] + incl - sum;
     for (int g = lo; g < hi; ++g) {
       sh.prefix[g] = run;
       run += group_tiles(seq_lens, g, rows, max_pages, skip_short);

@@ -78,7 +78,8 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
                         const int32_t* __restrict__ seq_lens,
                         const int32_t* __restrict__ block_table, int64_t bt_stride,
                         float* __restrict__ scores, int64_t score_stride, int batch, int num_pages,
-                        int max_pages, int skip_short, int32_t* status) {
+                        int max_pages, int skip_short, uint32_t* __restrict__ minmax,
+                        int32_t* status) {
   extern __shared__ unsigned char dyn_raw[];
   const uint32_t raw_addr = smem_u32(dyn_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -122,16 +123,29 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
     const int lo = min(batch, tid * chunk), hi = min(batch, lo + chunk);
     int sum = 0;
     for (int b = lo; b < hi; ++b) sum += tiles_of(seq_lens[b], max_pages, skip_short);
-    sh.partial[tid] = sum;
+    // exclusive scan of the per-thread sums: inside each warp by shuffles, then over the warps
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    if (lane == 31) sh.partial[warp] = incl;
     __syncthreads();
-    if (tid == 0) {
-      int run = 0;
-      for (int i = 0; i < kTcThreads; ++i) { int v = sh.partial[i]; sh.partial[i] = run; run += v; }
-      sh.prefix[batch] = run;
-      sh.abort_flag = 0;
+    if (warp == 0) {
+      const int nw = kTcThreads / 32;
+      int wsum = lane < nw ? sh.partial[lane] : 0, wincl = wsum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, wincl, o);
+        if (lane >= o) wincl += up;
+      }
+      if (lane < nw) sh.partial[lane] = wincl - wsum;   // tiles before this warp
+      if (lane == nw - 1) sh.prefix[batch] = wincl;
+      if (lane == 0) sh.abort_flag = 0;
     }
     __syncthreads();
-    int run = sh.partial[tid];
+    int run = sh.partial[warp] + incl - sum;
     for (int b = lo; b < hi; ++b) {
       sh.prefix[b] = run;
       run += tiles_of(seq_lens[b], max_pages, skip_short);
@@ -241,8 +255,20 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
       int stage = 0, phase = 0, acc = 0, aphase = 0;
       int b = locate(sh.prefix, batch, w0), next_change = w0, first_tile = 0, len = 0;
       float wreg[kIdxHeads];
+      // running max of the ordered score keys of the current request, and of their complements
+      // (= its min): handed to the selection so that it can bin the row without a sweep of its own
+      uint32_t key_max = 0u, key_min_inv = 0u;
+      auto flush_minmax = [&](int req) {
+        if (minmax != nullptr && lane == 0 && key_max != 0u) {
+          atomicMax(&minmax[2 * req], key_max);
+          atomicMax(&minmax[2 * req + 1], key_min_inv);
+        }
+        key_max = 0u;
+        key_min_inv = 0u;
+      };
       for (int w = w0; w < w1; ++w) {
         if (w >= next_change) {
+          if (w > w0) flush_minmax(b);
           while (sh.prefix[b + 1] <= w) ++b;
           next_change = sh.prefix[b + 1];
           first_tile = sh.prefix[b];
@@ -279,10 +305,17 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
           ptx::mbar_arrive(smem_u32(&sh.empty[stage]));
         }
         const int t = (w - first_tile) * kTcTile + rowi;
-        if (t < len) scores[(size_t)b * score_stride + t] = ((part[0] + part[1]) + (part[2] + part[3])) * sc;
+        const float val = ((part[0] + part[1]) + (part[2] + part[3])) * sc;
+        if (t < len) scores[(size_t)b * score_stride + t] = val;
+        if (minmax != nullptr) {
+          const uint32_t key = t < len ? float_to_ordered(fmaxf(val, kScoreFloor)) : 0u;
+          key_max = max(key_max, __reduce_max_sync(0xffffffffu, key));
+          key_min_inv = max(key_min_inv, __reduce_max_sync(0xffffffffu, t < len ? ~key : 0u));
+        }
         if (++stage == kTcStages) { stage = 0; phase ^= 1; }
         if (++acc == kTcAcc) { acc = 0; aphase ^= 1; }
       }
+      flush_minmax(b);
     }
   }
 #undef DSA_WAIT
@@ -308,7 +341,7 @@ cudaError_t launch_indexer_score_tc(const void* q_fp8, const void* k_cache, cons
                                     const int32_t* seq_lens, const int32_t* block_table,
                                     int64_t bt_stride, float* scores, int64_t score_stride,
                                     int batch, int num_pages, int max_pages, int skip_short,
-                                    int32_t* status, cudaStream_t stream) {
+                                    uint32_t* minmax, int32_t* status, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(indexer_score_tc_kernel,
@@ -338,7 +371,7 @@ cudaError_t launch_indexer_score_tc(const void* q_fp8, const void* k_cache, cons
         &cfg, indexer_score_tc_kernel, tmap_k, tmap_q, static_cast<const uint8_t*>(k_cache),
         weights + (size_t)b0 * kIdxHeads, seq_lens + b0, block_table + (size_t)b0 * bt_stride,
         bt_stride, scores + (size_t)b0 * score_stride, score_stride, nb, num_pages, max_pages,
-        skip_short, status);
+        skip_short, minmax != nullptr ? minmax + 2 * (size_t)b0 : nullptr, status);
     if (e != cudaSuccess) return e;
   }
   return cudaSuccess;

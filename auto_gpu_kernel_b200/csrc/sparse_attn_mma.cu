@@ -187,23 +187,27 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
   AtPartials part = at_carve(ws_raw, tokens, plan.segs_max);
 
   // ---------------- gather issue: tile `issued` goes to stage issued % 3 ------------------------
-  long ti = w0 / tpt;                 // (token, tile-in-token) of the next tile to issue
+  long ti = w0 / tpt;                 // (token, tile-in-token) of the tile whose indices are requested next
   int ji = (int)(w0 - ti * tpt);
-  int issued = 0, nv0 = -1, nv1 = -1; // its 64 indices, two per lane, requested one tile ahead
+  // indices of the next tile to issue (nv) and of the one after it (nw), two per lane: requested
+  // two tiles ahead so that no issue ever waits for its index row (the first two go out together)
+  int issued = 0, nv0 = -1, nv1 = -1, nw0 = -1, nw1 = -1;
   auto load_indices = [&](long tt, int jj, int& a, int& b) {
     const int k0 = jj * kAtTile + lane, k1 = k0 + 32;
     a = k0 < topk ? __ldg(indices + (size_t)tt * index_stride + k0) : -1;
     b = k1 < topk ? __ldg(indices + (size_t)tt * index_stride + k1) : -1;
   };
+  auto advance = [&]() { if (++ji == tpt) { ji = 0; ++ti; } };
   ptx::grid_dependency_wait();  // the index rows may come from the kernel before us in the stream
-  if (n > 0) load_indices(ti, ji, nv0, nv1);
+  if (n > 0) { load_indices(ti, ji, nv0, nv1); advance(); }
+  if (n > 1) { load_indices(ti, ji, nw0, nw1); advance(); }
   const int sub = lane >> 3, ch = lane & 7;  // row inside a 4-row group, 16-byte chunk of a 128-byte block
   auto issue_tile = [&]() {
     if (issued < n) {
       const int s = issued % kMmStages;
       int v0 = nv0, v1 = nv1;
-      if (++ji == tpt) { ji = 0; ++ti; }
-      if (issued + 1 < n) load_indices(ti, ji, nv0, nv1);
+      nv0 = nw0; nv1 = nw1;
+      if (issued + 2 < n) { load_indices(ti, ji, nw0, nw1); advance(); }
       if (v0 >= num_slots || v1 >= num_slots) {
         raise_status(status, DSA_STATUS_BAD_SLOT);
         if (v0 >= num_slots) v0 = -1;

@@ -35,7 +35,7 @@ constexpr int kSelRowCap = 45056;  // scores staged in dynamic shared memory (17
 constexpr int kSelBins = 2048;
 constexpr int kSelCandCap = 1024;
 constexpr int kSelTableCap = 2048;      // block_table entries staged in shared memory (128K tokens)
-constexpr float kSelFloor = -3.0e38f;  // -inf / NaN scores are ranked as this value
+constexpr float kSelFloor = kScoreFloor;  // -inf / NaN scores are ranked as this value
 
 struct SelShared {
   uint32_t hist[kSelBins];
@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(kSelThreads, 1)
 topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
                    const int32_t* __restrict__ seq_lens, const int32_t* __restrict__ block_table,
                    int64_t bt_stride, int32_t* __restrict__ out, int64_t out_stride, int max_pages,
-                   int32_t* status) {
+                   uint32_t* __restrict__ minmax, int32_t* status) {
   extern __shared__ float row_s[];
   __shared__ SelShared sh;
   cg::cluster_group cluster = cg::this_cluster();
@@ -129,6 +129,7 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   if (len <= kTopK) {  // every token is selected: no scores needed (uniform over the cluster)
     for (int i = crank * kSelThreads + tid; i < kTopK; i += csize * kSelThreads)
       out_row[i] = i < len ? table[i >> 6] * kPage + (i & 63) : -1;
+    if (minmax != nullptr && crank == 0 && tid == 0) { minmax[2 * b] = 0u; minmax[2 * b + 1] = 0u; }
     return;
   }
   if (table_staged) {
@@ -146,6 +147,24 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   ptx::launch_dependents();
   ptx::grid_dependency_wait();
 
+  // The scorer may have left the row's min / max (ordered keys, max of key and of ~key) next to the
+  // scores: then sweep A is not needed and the staging happens in sweep B.  Stale or foreign values
+  // would only cost speed: the bins stay monotone, out-of-range scores are clamped to the end bins.
+  uint32_t given_max = 0u, given_min_inv = 0u;
+  if (minmax != nullptr) {
+    given_max = minmax[2 * b];
+    given_min_inv = minmax[2 * b + 1];
+  }
+  const bool have_minmax = given_max != 0u && given_min_inv != 0u;   // uniform over the cluster
+  if (have_minmax) {
+    for (int i = tid; i < kSelBins; i += kSelThreads) sh.hist[i] = 0;
+    if (tid == 0) {
+      sh.cnt_gt2 = 0; sh.cnt_eq = 0; sh.cnt_cand = 0;
+      sh.kmin = __float_as_uint(ordered_to_float(~given_min_inv));
+      sh.kmax = __float_as_uint(ordered_to_float(given_max));
+    }
+    __syncthreads();
+  } else
   // ---- sweep A: stage the segment, min / max ----------------------------------------------------
   {
     float mn = INFINITY, mx = kSelFloor;
@@ -201,7 +220,9 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   const float span = __uint_as_float(sh.kmax) - lo;
   const float inv = span > 0.f ? (float)kSelBins / span : 0.f;
   auto bin_of = [&](float v) -> int {
-    return min(kSelBins - 1, __float2int_rz((fmaxf(v, kSelFloor) - lo) * inv));
+    // clamped at both ends (and NaN -> 0): with a [lo, hi] that does not come from this very row
+    // the map must still be monotone and stay inside the histogram
+    return min(kSelBins - 1, __float2int_rz(fmaxf((fmaxf(v, kSelFloor) - lo) * inv, 0.f)));
   };
 
   // ---- sweep B: histogram of the linear bins, summed over the cluster ---------------------------
@@ -210,9 +231,11 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   int* bin_s = reinterpret_cast<int*>(row_s);
   // four elements per thread and step: the loads, the bin arithmetic and the atomics of the four
   // are independent, which hides the shared-memory latency that a one-element loop exposes
-  const int n4s = staged ? (seg_len & ~3) : 0;
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
+  const int n4s = staged && (vec_ok || !have_minmax) ? (seg_len & ~3) : 0;
   for (int i = tid * 4; i < n4s; i += kSelThreads * 4) {
-    const float4 q = *reinterpret_cast<const float4*>(row_s + i);
+    const float4 q = have_minmax ? __ldg(reinterpret_cast<const float4*>(row + seg_lo + i))
+                                 : *reinterpret_cast<const float4*>(row_s + i);
     const int4 bq = make_int4(bin_of(q.x), bin_of(q.y), bin_of(q.z), bin_of(q.w));
     *reinterpret_cast<int4*>(bin_s + i) = bq;
     atomicAdd(&sh.hist[bq.x], 1u);
@@ -221,11 +244,15 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
     atomicAdd(&sh.hist[bq.w], 1u);
   }
   for (int i = seg_lo + n4s + tid; i < seg_hi; i += kSelThreads) {
-    const int bin = bin_of(value_at(i));
+    const int bin = bin_of(have_minmax ? __ldg(row + i) : value_at(i));
     if (staged) bin_s[i - seg_lo] = bin;
     atomicAdd(&sh.hist[bin], 1u);
   }
   cluster.sync();
+  if (have_minmax && crank == 0 && tid == 0) {   // every CTA of the cluster has read them: reset
+    minmax[2 * b] = 0u;
+    minmax[2 * b + 1] = 0u;
+  }
   for (int k = tid; k < kSelBins; k += kSelThreads) {
     uint32_t c = 0, below_me = 0;
     for (int r = 0; r < csize; ++r) {
@@ -400,8 +427,8 @@ static int select_cluster_size(int batch) {
 
 cudaError_t launch_topk_select(const float* scores, int64_t score_stride, const int32_t* seq_lens,
                                const int32_t* block_table, int64_t bt_stride, int32_t* out,
-                               int64_t out_stride, int batch, int max_pages, int32_t* status,
-                               cudaStream_t stream) {
+                               int64_t out_stride, int batch, int max_pages, uint32_t* minmax,
+                               int32_t* status, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(topk_select_kernel,
@@ -427,7 +454,7 @@ cudaError_t launch_topk_select(const float* scores, int64_t score_stride, const 
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   return cudaLaunchKernelEx(&cfg, topk_select_kernel, scores, score_stride, seq_lens, block_table,
-                            bt_stride, out, out_stride, max_pages, status);
+                            bt_stride, out, out_stride, max_pages, minmax, status);
 }
 
 }  // namespace dsa

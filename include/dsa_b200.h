@@ -70,7 +70,10 @@ const char* dsa_b200_error_string(int code);
  *                request shares one row: chunked prefill)
  *   topk_out     [batch,2048] int32, row stride `topk_stride` elements; receives
  *                min(2048,seq_len) global slot ids (page*64+offset) then -1
- *   workspace    >= dsa_indexer_workspace_bytes(batch,max_pages) bytes, 256-byte aligned
+ *   workspace    >= dsa_indexer_workspace_bytes(batch,max_pages) bytes, 256-byte aligned, zero-filled
+ *                once when created: two words per request (min / max of the row, left by the
+ *                scorer and put back to zero by the selection; 512 KB whatever the batch), then
+ *                the fp32 score rows
  * ------------------------------------------------------------------------------------------- */
 size_t dsa_indexer_workspace_bytes(int batch, int max_pages);
 

@@ -163,6 +163,53 @@ def test_prefill_scorer_ragged_lengths(cuda):
     assert_topk_matches(ragged, out, rows, label="prefill ragged")
 
 
+@pytest.mark.parametrize("junk", ["random", "ones", "nan", "tiny_range"])
+def test_foreign_minmax_words_cost_speed_not_correctness(cuda, junk):
+    """The scorer leaves each row's min / max in the workspace for the selection.  Whatever those
+    words hold when a call starts (an aborted call, a caller that did not zero the workspace), the
+    selected set stays exact: the bins are clamped and monotone for any [lo, hi]."""
+    lens = [3000, 2049, 40000, 9000]
+    inp = wl.make_indexer_inputs(lens, seed=17, device=cuda)
+    rows = [r.cpu() for r in oracle.indexer_scores(*inp.args())]
+    first = indexer.run(*inp.args())                       # creates the shared workspace
+    assert_topk_matches(inp, first, rows, label="clean")
+    lib_need = 512 * 1024
+    ws = workspace.get(cuda, "indexer", lib_need)
+    words = ws[:lib_need].view(torch.int32)
+    if junk == "random":
+        words.random_(-2**31, 2**31 - 1)
+    elif junk == "ones":
+        words.fill_(-1)
+    elif junk == "nan":
+        words.copy_(torch.full_like(words, 0x7FC00000 | (1 << 31) - (1 << 31)))   # key of a NaN
+    else:   # a [lo, hi] far above every score: everything falls into the lowest bin
+        key = torch.tensor([1.0e30], dtype=torch.float32).view(torch.int32).item() | -2**31
+        words[0::2] = key
+        words[1::2] = ~key
+    for attempt in range(2):    # the call that meets the junk, then the one after it
+        out = indexer.run(*inp.args())
+        workspace.check_status(cuda)
+        assert_topk_matches(inp, out, rows, label=f"{junk} attempt {attempt}")
+    torch.cuda.synchronize()
+    assert int(words[: 2 * len(lens)].abs().sum()) == 0     # put back to zero for the next call
+
+
+def test_rows_within_topk_need_no_scores(cuda):
+    """When no request can exceed 2048 tokens (max_pages <= 32) every cached token is selected and
+    the scorer is not launched: the result is the request's slots, whatever the keys are."""
+    lens = [0, 1, 63, 64, 700, 2047, 2048]
+    inp = wl.make_indexer_inputs(lens, seed=13, device=cuda)
+    assert inp.block_table.shape[1] == 32
+    inp.k_index_cache_fp8.view(torch.uint8).fill_(0xFF)      # NaN keys and scales: must not matter
+    out = indexer.run(*inp.args())
+    workspace.check_status(cuda)
+    for b, n in enumerate(lens):
+        want = (inp.block_table[b, torch.arange(n, device=cuda) // 64].long() * 64
+                + torch.arange(n, device=cuda) % 64)
+        assert torch.equal(out[b, :n].long().sort().values, want.sort().values)
+        assert (out[b, n:] == -1).all()
+
+
 def test_cpu_tensors_are_rejected():
     inp = wl.make_indexer_inputs([100], seed=0)
     with pytest.raises(RuntimeError, match="no CPU path"):
