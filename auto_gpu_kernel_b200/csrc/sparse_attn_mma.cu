@@ -178,9 +178,8 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
     w0 = tok * tpt + (long)rank * tpt / csize;
     w1 = tok * tpt + (long)(rank + 1) * tpt / csize;
   } else {
-    w0 = plan.balanced ? plan.starts[blockIdx.x] : (long)blockIdx.x * plan.per_cta;
-    w1 = plan.balanced ? plan.starts[blockIdx.x + 1]
-                       : (w0 + plan.per_cta < total ? w0 + plan.per_cta : total);
+    w0 = (long)blockIdx.x * plan.per_cta;
+    w1 = w0 + plan.per_cta < total ? w0 + plan.per_cta : total;
   }
   const int n = (int)(w1 - w0);
   if (!kCluster && n <= 0) return;
@@ -395,8 +394,7 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
 #pragma unroll
       for (int ww = 0; ww < 8; ++ww) { lt0 += sh.red[ww][g]; lt1 += sh.red[ww][g + 8]; }
       const long first_tile = t * tpt, last_tile = first_tile + tpt - 1;
-      const int cta_first = plan.balanced ? at_owner(plan, first_tile) : (int)(first_tile / plan.per_cta);
-      const int cta_last = plan.balanced ? at_owner(plan, last_tile) : (int)(last_tile / plan.per_cta);
+      const int cta_first = (int)(first_tile / plan.per_cta), cta_last = (int)(last_tile / plan.per_cta);
       const int n_seg = cta_last - cta_first + 1, seg = (int)blockIdx.x - cta_first;
       const int col = 64 * w + 2 * t4;
       if (n_seg == 1) {
@@ -594,21 +592,12 @@ cudaError_t launch_sparse_attn_mma(const void* q_nope, const void* q_pe, const v
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  static double start_cost = -1.0;
-  static int balanced = -1, cluster_ok = -1;
-  if (balanced < 0) {
-    // The cost-balanced contiguous split was measured equal to the uniform one at the headline
-    // shape (40.5-42 us for start costs 1-5 against 41.7 us).  DSA_ATT_BALANCED=1 enables it,
-    // DSA_ATT_CLUSTER=0 turns the cluster-per-token split off.
-    const char* e = getenv("DSA_ATT_START_COST");
-    start_cost = e != nullptr ? atof(e) : 1.0;
-    e = getenv("DSA_ATT_BALANCED");
-    balanced = (e != nullptr && e[0] == '1') ? 1 : 0;
-    e = getenv("DSA_ATT_CLUSTER");
+  static int cluster_ok = -1;
+  if (cluster_ok < 0) {   // DSA_ATT_CLUSTER=0 forces the contiguous-range split (for A/B timing)
+    const char* e = getenv("DSA_ATT_CLUSTER");
     cluster_ok = (e != nullptr && e[0] == '0') ? 0 : 1;
   }
-  AtPlan plan = at_make_plan(tokens, topk, sm_count(), start_cost);
-  if (!balanced) plan.balanced = 0;
+  AtPlan plan = at_make_plan(tokens, topk, sm_count());
   const int csize = cluster_ok ? mm_cluster_size(tokens, plan.tiles_per_token, sm_count()) : 0;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kMmThreads);
@@ -621,7 +610,6 @@ cudaError_t launch_sparse_attn_mma(const void* q_nope, const void* q_pe, const v
   cfg.numAttrs = 1;
   if (csize > 0) {
     plan.per_cta = csize;   // the kernel reads the cluster size from here
-    plan.balanced = 0;
     cfg.gridDim = dim3((unsigned)(tokens * csize));
     attr[1].id = cudaLaunchAttributeClusterDimension;
     attr[1].val.clusterDim.x = (unsigned)csize;

@@ -656,7 +656,6 @@ cudaError_t launch_sparse_attn_tc(const void* q_nope, const void* q_pe, const vo
     attr_set = true;
   }
   AtPlan plan = at_make_plan(tokens, topk, sm_count());
-  plan.balanced = 0;  // this kernel uses the uniform split only
   sparse_attn_tc_kernel<<<plan.grid, kAtThreads, kAtDynBytes, stream>>>(
       static_cast<const __nv_bfloat16*>(q_nope), static_cast<const __nv_bfloat16*>(q_pe),
       static_cast<const __nv_bfloat16*>(ckv), static_cast<const __nv_bfloat16*>(kpe), indices,
