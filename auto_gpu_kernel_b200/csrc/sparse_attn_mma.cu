@@ -18,7 +18,9 @@
 //     conflict-free; masked rows (-1) are zero-filled.  (An L2 prefetch stream of bulk prefetches a
 //     few tiles ahead was tried on top: 56-69 us instead of 42-44 us.)  (Fetching rows with cp.async.bulk, 1024 B +
 //     128 B per row into linear padded rows, was measured at 92.7 us for the headline shape against
-//     50.5 us for these 16-byte copies: the bulk engine costs ~70 cycles per request.);
+//     50.5 us for these 16-byte copies: the bulk engine costs ~70 cycles per request.  Handing two or
+//     three of the nine column blocks to TMA tile::gather4 next to the cp.async copies was slower as
+//     well (decode 36.1-37.4 us against 35.1 us; 4096-token prefill 1.81-1.85 ms against 1.54 ms).);
 //   * S[16 heads, 64 rows] = Q.K^T: warp w owns rows 8w..8w+7; q lives in registers as the 36
 //     A fragments of the token (loaded once per token), K fragments come from ldmatrix.x4;
 //   * online softmax in base 2 with a lazily refreshed running max (refreshed, and O rescaled in
