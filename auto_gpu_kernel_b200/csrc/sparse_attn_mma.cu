@@ -15,12 +15,12 @@
 //   * three 64-row stages in shared memory, filled by cp.async 16-byte copies issued by all warps
 //     two tiles ahead; a tile is nine [64 rows x 128 B] blocks (8 ckv column blocks + kpe) with the
 //     16-byte chunks of a row XOR-swizzled by (row & 7), so both ldmatrix patterns below are
-//     conflict-free; masked rows (-1) are zero-filled.  (An L2 prefetch stream of bulk prefetches a
-//     few tiles ahead was tried on top: 56-69 us instead of 42-44 us.)  (Fetching rows with cp.async.bulk, 1024 B +
-//     128 B per row into linear padded rows, was measured at 92.7 us for the headline shape against
-//     50.5 us for these 16-byte copies: the bulk engine costs ~70 cycles per request.  Handing two or
-//     three of the nine column blocks to TMA tile::gather4 next to the cp.async copies was slower as
-//     well (decode 36.1-37.4 us against 35.1 us; 4096-token prefill 1.81-1.85 ms against 1.54 ms).);
+//     conflict-free; masked rows (-1) are zero-filled.  Measured alternatives for the gather, all
+//     slower at the headline shape (64 tokens): cp.async.bulk per row into linear padded rows
+//     (92.7 us against 50.5 us at the time: ~70 cycles per bulk request), an L2 bulk-prefetch stream a
+//     few tiles ahead (56-69 us against 42-44 us), two or three of the nine blocks by TMA
+//     tile::gather4 next to the cp.async copies (36.1-37.4 us against 35.1 us; 4096-token prefill
+//     1.81-1.85 ms against 1.54 ms);
 //   * S[16 heads, 64 rows] = Q.K^T: warp w owns rows 8w..8w+7; q lives in registers as the 36
 //     A fragments of the token (loaded once per token), K fragments come from ldmatrix.x4;
 //   * online softmax in base 2 with a lazily refreshed running max (refreshed, and O rescaled in
