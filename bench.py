@@ -31,7 +31,7 @@ sys.path.insert(0, str(ROOT))
 BATCH = 64
 CONTEXT = 32768
 TOPK = 2048
-SCORER_DRAM_BYTES_PER_TOKEN = (138866432 + 1330432) / (32 * 32768)
+SCORER_DRAM_BYTES_PER_TOKEN = (138860544 + 1302784) / (32 * 32768)
 METRIC = "us/call: DSA indexer + sparse attn, decode B=64 ctx 32K"
 WORKLOAD = "dsa_decode_block B=64/GPU ctx=32768 ps=64 topk=2048 (indexer 64h fp8 -> sparse MLA 16h bf16)"
 
