@@ -177,8 +177,12 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
         const int len = max(0, min(seq_lens[bi], max_pages * kPage));
         const int n_pages = (len + kPage - 1) / kPage;
         const int32_t* row = block_table + (size_t)bi * bt_stride + 2 * ji;
+        // both entries are requested at once (the row has max_pages entries, so the second read is
+        // in bounds); whether the second page belongs to the request is decided afterwards, so the
+        // lookup costs one round trip, not two
         int p0 = row[0];
-        int p1 = (2 * ji + 1 < n_pages) ? row[1] : -1;
+        int p1 = (2 * ji + 1 < max_pages) ? row[1] : -1;
+        if (2 * ji + 1 >= n_pages) p1 = -1;
         if (p0 < 0 || p0 >= num_pages) { raise_status(status, DSA_STATUS_BAD_PAGE); p0 = 0; }
         if (p1 >= num_pages) { raise_status(status, DSA_STATUS_BAD_PAGE); p1 = 0; }
         const int n = min(32, w1 - w);
