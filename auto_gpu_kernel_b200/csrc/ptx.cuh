@@ -63,18 +63,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, 
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
-// Gather of four rows of a 2-D tensor (row indices r0..r3, columns starting at x) into four
-// consecutive 128-byte rows of shared memory; the tensor map's box is {64 elements, 1 row}.  Rows
-// outside the tensor (e.g. index -1) are filled with zeros.  No multicast.
-__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* m, int32_t x, int32_t r0,
-                                            int32_t r1, int32_t r2, int32_t r3, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3),
-        "r"(bar)
-      : "memory");
-}
 // 1-D bulk copy global -> shared; src/dst 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes,
                                              uint32_t bar) {
@@ -151,18 +139,9 @@ __device__ __forceinline__ void mma_f8(uint32_t d_tmem, uint64_t adesc, uint64_t
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc_v), "r"(acc)
       : "memory");
 }
-__device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                         uint32_t idesc_v, bool accumulate) {
-  uint32_t acc = accumulate ? 1u : 0u;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc_v), "r"(acc)
-      : "memory");
-}
-
-// Same with the descriptors split in (low, high) 32-bit halves: the 14-bit address field lives in
-// the low half, so stepping through a tile is one 32-bit add on `*_lo` per instruction.
+// kind::f16 (bf16 inputs) with the descriptors split in (low, high) 32-bit halves: the 14-bit
+// address field lives in the low half, so stepping through a tile is one 32-bit add on `*_lo` per
+// instruction.
 __device__ __forceinline__ void mma_bf16_split(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
                                                uint32_t b_lo, uint32_t b_hi, uint32_t idesc_v,
                                                uint32_t accumulate) {
@@ -238,14 +217,6 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 // `launch_dependents` lets the successor start early (its own wait still protects the data).
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(pred));
-  return pred != 0;
-}
 
 }  // namespace ptx
 }  // namespace dsa
