@@ -73,7 +73,7 @@ def gather_indices(local_indices: torch.Tensor, counts, group=None) -> torch.Ten
 def decode_block_head_sharded(idx_args_local, counts, q_nope_heads, q_pe_heads, ckv_cache, kpe_cache,
                               sm_scale, output, lse, local_indices=None, group=None, indexer_fn=None,
                               attention_fn=None):
-    """Head-sharded layout of BASELINE's full 128-head block.
+    """Head-sharded layout of the full 128-head block (128 heads = 8 ranks x 16).
 
     idx_args_local : indexer inputs of this rank's request shard (q, cache, weights, seq_lens,
                      block_table); the cache holds (at least) this shard's pages

@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
 
 One "step" = one call of the indexer followed by one call of sparse attention over the indices it
-produced, on BASELINE's headline decode point: B = 64 requests per GPU, context 32768, page size
+produced, on the headline decode point: B = 64 requests per GPU, context 32768, page size
 64, top-k 2048.  With N > 1 (torchrun, one rank per GPU) requests are sharded: every rank owns its
 own 64 requests and their cache pages, there is no data-path collective, and the reported time is
 the maximum over ranks (weak scaling).  Prints ONE JSON line on rank 0.
@@ -137,7 +137,7 @@ def block_to_cpu(block):
 
 # ------------------------------------------------------------------------------ head-sharded block
 def run_head_sharded(args, rank, world, dev):
-    """BASELINE's full-block layout: B = 128 requests, ctx uniform in [16K, 64K]; the indexer is
+    """The full-block layout: B = 128 requests, ctx uniform in [16K, 64K]; the indexer is
     request-sharded, its int32 [B, 2048] index rows are all-gathered (NCCL), attention runs for all
     tokens on every rank for that rank's 16 heads over replicated ckv/kpe caches."""
     import torch.distributed as dist
@@ -220,7 +220,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layout", default="requests", choices=["requests", "heads"],
                     help="requests: every rank owns its requests, no collective (default, the headline "
-                         "metric); heads: BASELINE's full 128-head block -- indexer request-sharded, "
+                         "metric); heads: the full 128-head block -- indexer request-sharded, "
                          "all-gather of the index rows, attention head-sharded")
     ap.add_argument("--batch", type=int, default=BATCH, help=argparse.SUPPRESS)
     ap.add_argument("--context", type=int, default=CONTEXT, help=argparse.SUPPRESS)

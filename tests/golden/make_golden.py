@@ -104,7 +104,9 @@ def cache_write_case(ref, name, seed):
 def main():
     args = [a for a in sys.argv[1:] if not a.startswith("--only=")]
     only = [a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--only=")]
-    root = Path(args[0] if args else "/root/reference")
+    if not args:
+        sys.exit(__doc__)
+    root = Path(args[0])
     if only == ["cache_write"]:
         idx_ref = _load(root / IDX_REL, "ref_indexer_baseline")
         cache_write_case(idx_ref, "cache_write", seed=5)
@@ -112,7 +114,7 @@ def main():
     torch.manual_seed(0)
     idx_ref = _load(root / IDX_REL, "ref_indexer_baseline")
     att_ref = _load(root / ATT_REL, "ref_sparse_baseline")
-    # BASELINE configs[0]: the reference's own CPU-runnable case.
+    # The reference's own CPU-runnable case: 4 requests of 1024..4096 tokens.
     indexer_case(idx_ref, "indexer_cfg0", [1024, 2048, 3000, 4096], seed=0)
     # Ragged/edge lengths: empty request, single token, page boundary +-1, just over top-k.
     indexer_case(idx_ref, "indexer_edges", [0, 1, 63, 64, 65, 2047, 2049, 2500], seed=1)

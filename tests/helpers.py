@@ -9,7 +9,7 @@ from auto_gpu_kernel_b200 import inputs as wl
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
-# Tolerances of the acceptance rule (BASELINE north_star): attention output atol = rtol = 1e-2
+# Tolerances of the acceptance rule: attention output atol = rtol = 1e-2
 # (bf16), LSE 1e-3; indexer: exact set where the boundary gap > 1e-3 relative, else recall >= 0.999
 # and selected scores within 1e-3.
 ATT_ATOL = 1e-2

@@ -1,4 +1,4 @@
-"""BASELINE.json's configurations at their full sizes, checked through size-independent properties
+"""The benchmark configurations at their full sizes, checked through size-independent properties
 and against the oracle on a sample of rows (the oracle runs on the GPU in fp32 where the CPU would
 take minutes)."""
 import pytest
