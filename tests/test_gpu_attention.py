@@ -63,6 +63,21 @@ def test_cluster_split_token_counts(cuda, tokens):
 
 
 @VARIANTS
+@pytest.mark.parametrize("topk", [1, 64, 100, 512, 1000, 2047])
+def test_other_index_widths(cuda, topk, variant):
+    """The C ABI takes the width of the index rows as an argument: widths that are not the
+    definition's 2048, including ones that are not multiples of the 64-row tile."""
+    for tokens in (3, 20, 70, 140):
+        inp = wl.make_attention_inputs([6000] * tokens, seed=31 * tokens + topk, device=cuda)
+        inp.sparse_indices = inp.sparse_indices[:, :topk].contiguous()
+        out, lse = sparse_attention.run(*inp.args(), variant=variant)
+        workspace.check_status(cuda)
+        ref_out, ref_lse = oracle.sparse_attention(*inp.args(), output=torch.empty_like(out),
+                                                   lse=torch.empty_like(lse))
+        assert_attention_close(out, lse, ref_out.cpu(), ref_lse.cpu(), label=f"topk={topk} T={tokens}")
+
+
+@VARIANTS
 def test_token_count_changes_between_calls(cuda, variant):
     """One workspace serves calls of different token counts: the arrival counters of one call must
     never sit where an earlier call with another token count left partial results."""
