@@ -194,6 +194,24 @@ def test_foreign_minmax_words_cost_speed_not_correctness(cuda, junk):
     assert int(words[: 2 * len(lens)].abs().sum()) == 0     # put back to zero for the next call
 
 
+def test_strided_block_table_and_output_rows(cuda):
+    """block_table and topk_indices may be column slices of wider tensors (row stride larger than
+    the row length): the reference's kernels take the strides as arguments too."""
+    lens = [2500, 7000, 64, 3000, 2049]
+    inp = wl.make_indexer_inputs(lens, seed=23, device=cuda)
+    pages = inp.block_table.shape[1]
+    wide_table = torch.full((len(lens), pages + 37), -5, dtype=torch.int32, device=cuda)
+    wide_table[:, :pages] = inp.block_table
+    wide_out = torch.full((len(lens), 2048 + 64), -9, dtype=torch.int32, device=cuda)
+    table_view, out_view = wide_table[:, :pages], wide_out[:, :2048]
+    assert table_view.stride(0) == pages + 37 and out_view.stride(0) == 2048 + 64
+    indexer.kernel(inp.q_index_fp8, inp.k_index_cache_fp8, inp.weights, inp.seq_lens, table_view, out_view)
+    workspace.check_status(cuda)
+    rows = [r.cpu() for r in oracle.indexer_scores(*inp.args())]
+    assert_topk_matches(inp, out_view.contiguous(), rows, label="strided")
+    assert (wide_out[:, 2048:] == -9).all()          # nothing written past a row
+
+
 def test_rows_within_topk_need_no_scores(cuda):
     """When no request can exceed 2048 tokens (max_pages <= 32) every cached token is selected and
     the scorer is not launched: the result is the request's slots, whatever the keys are."""
