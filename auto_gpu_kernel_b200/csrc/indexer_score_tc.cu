@@ -89,7 +89,6 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
   TcShared& sh = *reinterpret_cast<TcShared*>(base + kTcStages * kTileDataBytes + 2 * kPageDataBytes);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  ptx::launch_dependents();  // the selection kernel may be scheduled as SMs free up; it waits for our scores
 
   // set-up that reads nothing from global memory, so that it can overlap the tail of the kernel
   // before us in the stream (programmatic dependent launch)
@@ -116,6 +115,9 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
     ptx::tmem_relinquish();
   }
   ptx::grid_dependency_wait();  // q, weights, seq_lens, block_table and the cache may come from it
+  // Only now may the selection kernel be scheduled (as SMs free up; it waits for our scores): it
+  // reads seq_lens and block_table before its own wait, which is safe once OUR predecessor is done.
+  ptx::launch_dependents();
 
   // ---- tiles per request -> exclusive prefix (all threads) ------------------------------------
   {

@@ -171,7 +171,6 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
   const int tpt = plan.tiles_per_token;
-  ptx::launch_dependents();   // the next kernel in the stream may run its set-up under our tail
   const long total = (long)tokens * tpt;
   long w0, w1;
   if (kCluster) {   // plan.per_cta holds the cluster size: rank r takes the r-th share of the token's tiles
@@ -200,6 +199,7 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
   };
   auto advance = [&]() { if (++ji == tpt) { ji = 0; ++ti; } };
   ptx::grid_dependency_wait();  // the index rows may come from the kernel before us in the stream
+  ptx::launch_dependents();     // from here on the next kernel in the stream may run its set-up under our tail
   if (n > 0) { load_indices(ti, ji, nv0, nv1); advance(); }
   if (n > 1) { load_indices(ti, ji, nw0, nw1); advance(); }
   const int sub = lane >> 3, ch = lane & 7;  // row inside a 4-row group, 16-byte chunk of a 128-byte block
