@@ -143,7 +143,9 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   const bool staged = seg <= kSelRowCap;
   auto value_at = [&](int i) -> float { return staged ? row_s[i - seg_lo] : __ldg(row + i); };
 
-  // everything above only read the caller's inputs; the scores come from the kernel before us
+  // everything above only read the caller's inputs; the scores come from the kernel before us.
+  // The successor (the attention kernel: it reads nothing before its own wait) may be scheduled
+  // already while we wait for the scorer.
   ptx::launch_dependents();
   ptx::grid_dependency_wait();
 
