@@ -1,6 +1,7 @@
 // extern "C" boundary of libdsa_b200.so: argument checks on the host, then kernel launches on the
 // caller's stream.  No allocation, no synchronisation, no exceptions cross this boundary.
 #include <cstdio>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -10,9 +11,15 @@ cudaError_t launch_indexer_score_simt(const void*, const void*, const float*, co
                                       int32_t*, cudaStream_t);
 cudaError_t launch_indexer_score_tc(const void*, const void*, const float*, const int32_t*,
                                     const int32_t*, int64_t, float*, int64_t, int, int, int, int,
-                                    uint32_t*, int32_t*, cudaStream_t);
+                                    uint32_t*, uint32_t*, int32_t*, cudaStream_t);
+cudaError_t launch_topk_select_hist(const float*, int64_t, const int32_t*, const int32_t*, int64_t,
+                                    int32_t*, int64_t, int, int, uint32_t*, int32_t*, cudaStream_t);
+bool topk_select_hist_supports(int batch, int max_pages);
 cudaError_t launch_topk_select(const float*, int64_t, const int32_t*, const int32_t*, int64_t,
                                int32_t*, int64_t, int, int, uint32_t*, int32_t*, cudaStream_t);
+cudaError_t launch_indexer_topk_fused(const void*, const void*, const float*, const int32_t*,
+                                      const int32_t*, int64_t, float*, int64_t, int32_t*, int64_t,
+                                      int, int, int, uint32_t*, uint32_t*, int32_t*, cudaStream_t);
 cudaError_t launch_sparse_attn_simt(const void*, const void*, const void*, const void*,
                                     const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
                                     int, void*, int32_t*, cudaStream_t);
@@ -62,20 +69,39 @@ const char* dsa_b200_error_string(int code) {
   return "dsa_b200: unknown error code";
 }
 
-// [ per request: max of the ordered score keys, max of their complements | fp32 score rows ]
-// The min / max words must be zero between calls (the selection puts them back), so their region
+// [ per request: max of the ordered score keys, max of their complements | control words and
+//   per-request histograms of the fused kernel | fp32 score rows ]
+// The first two regions must be zero between calls (the kernels put back what they use), so each
 // has one fixed size for every shape: no call's score rows ever land on another call's words.
 constexpr size_t kMinmaxRegionBytes = 65536 * 2 * sizeof(uint32_t);   // batch <= 65535
+constexpr size_t kScoreRowsOffset = kMinmaxRegionBytes + dsa::kFusedRegionBytes;
 size_t dsa_indexer_workspace_bytes(int batch, int max_pages) {
   if (batch <= 0 || max_pages <= 0) return 256;
-  return kMinmaxRegionBytes + round256((size_t)batch * score_row_stride(max_pages) * sizeof(float));
+  return kScoreRowsOffset + round256((size_t)batch * score_row_stride(max_pages) * sizeof(float));
+}
+
+// How dsa_indexer_topk scores and selects long rows (decode shapes, batch <= 1024):
+//   "hist"   (default) the scorer also builds every request's score histogram; the selection
+//            kernel starts from it (boundary bin, one counting and one writing sweep);
+//   "fused"  one kernel: requests are selected inside the scorer as their last chunk completes;
+//   "minmax" the scorer hands over each row's min / max, the selection builds its own histogram
+//            (also what larger batches and the shared-pages scorer use).
+// DSA_INDEXER_PATH in the environment picks one; read on every call so that a test can compare
+// the paths in one process.
+enum IndexerPath { kPathHist, kPathFused, kPathMinmax };
+static IndexerPath indexer_path() {
+  const char* e = getenv("DSA_INDEXER_PATH");
+  if (e == nullptr) return kPathHist;
+  if (e[0] == 'f') return kPathFused;
+  if (e[0] == 'm') return kPathMinmax;
+  return kPathHist;
 }
 
 static int scores_impl(const void* q_fp8, const void* k_cache, const float* weights,
                        const int32_t* seq_lens, const int32_t* block_table,
                        int64_t block_table_stride, float* scores, int64_t score_stride, int batch,
                        int num_pages, int max_pages, int variant, int skip_short, uint32_t* minmax,
-                       int32_t* status_dev, void* stream) {
+                       uint32_t* ghist, int32_t* status_dev, void* stream) {
   if (batch == 0) return DSA_OK;
   if (!q_fp8 || !k_cache || !weights || !seq_lens || !block_table || !scores)
     return DSA_ERR_NULL_POINTER;
@@ -98,7 +124,7 @@ static int scores_impl(const void* q_fp8, const void* k_cache, const float* weig
   } else if (variant == 0 || variant == 2) {
     e = dsa::launch_indexer_score_tc(q_fp8, k_cache, weights, seq_lens, block_table,
                                      block_table_stride, scores, score_stride, batch, num_pages,
-                                     max_pages, skip_short, minmax, status_dev, s);
+                                     max_pages, skip_short, minmax, ghist, status_dev, s);
   } else {
     return DSA_ERR_UNSUPPORTED;
   }
@@ -111,7 +137,8 @@ int dsa_indexer_scores(const void* q_fp8, const void* k_cache, const float* weig
                        int num_pages, int max_pages, int variant, int32_t* status_dev,
                        void* stream) {
   return scores_impl(q_fp8, k_cache, weights, seq_lens, block_table, block_table_stride, scores,
-                     score_stride, batch, num_pages, max_pages, variant, 0, nullptr, status_dev, stream);
+                     score_stride, batch, num_pages, max_pages, variant, 0, nullptr, nullptr, status_dev,
+                     stream);
 }
 
 int dsa_topk_select(const float* scores, int64_t score_stride, const int32_t* seq_lens,
@@ -139,18 +166,46 @@ int dsa_indexer_topk(const void* q_fp8, const void* k_cache, const float* weight
     return DSA_ERR_WORKSPACE_TOO_SMALL;
   if (reinterpret_cast<uintptr_t>(workspace) & 255u) return DSA_ERR_MISALIGNED;
   if (batch > 65535) return DSA_ERR_BAD_SHAPE;
-  float* scores = reinterpret_cast<float*>(static_cast<char*>(workspace) + kMinmaxRegionBytes);
+  float* scores = reinterpret_cast<float*>(static_cast<char*>(workspace) + kScoreRowsOffset);
   const int64_t stride = score_row_stride(max_pages);
   // The streaming scorer leaves every row's min / max in front of the score rows (the words start
   // at zero and the selection puts them back to zero); the shared-pages scorer does not.
   const bool shared_pages = block_table_stride == 0 && batch >= dsa::kPrefillMinRows;
   uint32_t* minmax = shared_pages ? nullptr : static_cast<uint32_t*>(workspace);
+  const bool long_rows = (int64_t)max_pages * dsa::kPage > dsa::kTopK;
+  const IndexerPath path = indexer_path();
+  uint32_t* ghist = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + kMinmaxRegionBytes +
+                                                dsa::kFusedCtlBytes);
+  if (long_rows && !shared_pages && batch <= dsa::kFusedMaxBatch && path == kPathFused) {
+    // decode shapes: one kernel scores and selects (requests are selected as they complete,
+    // under the key stream of the later ones)
+    if (!q_fp8 || !k_cache || !weights || !seq_lens || !block_table || !topk_out)
+      return DSA_ERR_NULL_POINTER;
+    if (num_pages <= 0 || topk_stride < dsa::kTopK || block_table_stride < 0) return DSA_ERR_BAD_SHAPE;
+    if (!aligned16(q_fp8) || !aligned16(k_cache)) return DSA_ERR_MISALIGNED;
+    uint32_t* ctl = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + kMinmaxRegionBytes);
+    return static_cast<int>(dsa::launch_indexer_topk_fused(
+        q_fp8, k_cache, weights, seq_lens, block_table, block_table_stride, scores, stride, topk_out,
+        topk_stride, batch, num_pages, max_pages, ctl, ghist, status_dev,
+        static_cast<cudaStream_t>(stream)));
+  }
   // rows of at most 2048 tokens are emitted whole by the selection: their scores are skipped, and
   // when no row can be longer (max_pages <= 32) the scorer is not launched at all (the reference's
   // GPU dispatch takes the same shortcut from the shape alone, indexer_fused.py:358-380)
-  if ((int64_t)max_pages * dsa::kPage > dsa::kTopK) {
+  if (long_rows && !shared_pages && path != kPathMinmax &&
+      dsa::topk_select_hist_supports(batch, max_pages)) {
+    if (!topk_out) return DSA_ERR_NULL_POINTER;
+    if (topk_stride < dsa::kTopK) return DSA_ERR_BAD_SHAPE;
     int rc = scores_impl(q_fp8, k_cache, weights, seq_lens, block_table, block_table_stride, scores,
-                         stride, batch, num_pages, max_pages, 0, 1, minmax, status_dev, stream);
+                         stride, batch, num_pages, max_pages, 0, 1, nullptr, ghist, status_dev, stream);
+    if (rc != DSA_OK) return rc;
+    return static_cast<int>(dsa::launch_topk_select_hist(
+        scores, stride, seq_lens, block_table, block_table_stride, topk_out, topk_stride, batch,
+        max_pages, ghist, status_dev, static_cast<cudaStream_t>(stream)));
+  }
+  if (long_rows) {
+    int rc = scores_impl(q_fp8, k_cache, weights, seq_lens, block_table, block_table_stride, scores,
+                         stride, batch, num_pages, max_pages, 0, 1, minmax, nullptr, status_dev, stream);
     if (rc != DSA_OK) return rc;
   } else if (!q_fp8 || !k_cache || !weights || !seq_lens || !block_table) {
     return DSA_ERR_NULL_POINTER;

@@ -223,9 +223,10 @@ indexer_score_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k,
           longest = max(longest, clamp_len(seq_lens[r], max_pages));
         const int n_pages = (longest + kPage - 1) / kPage;   // later entries of block_row are not ids
         int p0 = block_row[2 * ji];
-        int p1 = (2 * ji + 1 < n_pages) ? block_row[2 * ji + 1] : -1;
+        const bool has_second = 2 * ji + 1 < n_pages;
+        int p1 = has_second ? block_row[2 * ji + 1] : -1;
         if (p0 < 0 || p0 >= num_pages) { raise_status(status, DSA_STATUS_BAD_PAGE); p0 = 0; }
-        if (p1 >= num_pages) { raise_status(status, DSA_STATUS_BAD_PAGE); p1 = 0; }
+        if (has_second && (p1 < 0 || p1 >= num_pages)) { raise_status(status, DSA_STATUS_BAD_PAGE); p1 = 0; }
         const int n = min(32, w1 - w);
         for (int i = 0; i < n; ++i) {
           const int tg = __shfl_sync(0xffffffffu, gi, i);
@@ -393,13 +394,11 @@ cudaError_t launch_indexer_score_prefill(const void* q_fp8, const void* k_cache,
                                          int64_t score_stride, int rows, int num_pages,
                                          int max_pages, int skip_short, int32_t* status,
                                          cudaStream_t stream) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(indexer_score_prefill_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)kPfDynBytes);
+  static std::atomic<uint64_t> smem_opted{0};
+  {
+    cudaError_t e = opt_in_dynamic_smem(reinterpret_cast<const void*>(indexer_score_prefill_kernel),
+                                        kPfDynBytes, smem_opted);
     if (e != cudaSuccess) return e;
-    attr_set = true;
   }
   CUtensorMap tmap_k;
   if (!make_tmap_2d_sw128(&tmap_k, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, k_cache, 128,

@@ -42,12 +42,14 @@ constexpr uint32_t kIdescF8 = ptx::idesc(ptx::kFmtE4M3, ptx::kFmtE4M3, false, fa
 
 struct TcShared {
   // data[stage] and q[slot] sit in the 1024-byte aligned dynamic region before this struct
+  alignas(16) uint32_t hist[kFusedBins];   // kHist: counts of the current request's scores per key bin
   float scale[kTcStages][kTcTile];
   int prefix[kTcMaxBatch + 1];
   int partial[kTcThreads];
   uint64_t full[kTcStages], empty[kTcStages];
   uint64_t qfull[2], qempty[2];
   uint64_t accfull[kTcAcc], accempty[kTcAcc];
+  uint64_t group;                          // kHist: barrier of the four epilogue warps
   uint32_t tmem_base;
   volatile int abort_flag;
 };
@@ -71,6 +73,10 @@ __device__ __forceinline__ int locate(const int* prefix, int batch, int w) {
   return lo;
 }
 
+// kHist: the epilogue also counts every score into a 4096-bin histogram over the top 12 bits of its
+// order-preserving key (shared memory, added to the request's histogram in `ghist` when the CTA
+// moves on to another request): the selection kernel then starts from the finished histogram.
+template <bool kHist>
 __global__ void __launch_bounds__(kTcThreads, 2)
 indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
                         const __grid_constant__ CUtensorMap tmap_q,
@@ -79,7 +85,7 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
                         const int32_t* __restrict__ block_table, int64_t bt_stride,
                         float* __restrict__ scores, int64_t score_stride, int batch, int num_pages,
                         int max_pages, int skip_short, uint32_t* __restrict__ minmax,
-                        int32_t* status) {
+                        uint32_t* __restrict__ ghist, int32_t* status) {
   extern __shared__ unsigned char dyn_raw[];
   const uint32_t raw_addr = smem_u32(dyn_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -106,6 +112,7 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
         ptx::mbar_init(smem_u32(&sh.accfull[i]), 1);
         ptx::mbar_init(smem_u32(&sh.accempty[i]), 4);
       }
+      ptx::mbar_init(smem_u32(&sh.group), 4);
       ptx::fence_barrier_init();
       ptx::prefetch_tensormap(&tmap_k);
       ptx::prefetch_tensormap(&tmap_q);
@@ -113,6 +120,9 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
     __syncwarp();
     ptx::tmem_alloc(smem_u32(&sh.tmem_base), kTcTmemCols);
     ptx::tmem_relinquish();
+  }
+  if (kHist) {
+    for (int i = tid; i < kFusedBins; i += kTcThreads) sh.hist[i] = 0;
   }
   ptx::grid_dependency_wait();  // q, weights, seq_lens, block_table and the cache may come from it
   // Only now may the selection kernel be scheduled (as SMs free up; it waits for our scores): it
@@ -184,9 +194,14 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
         // lookup costs one round trip, not two
         int p0 = row[0];
         int p1 = (2 * ji + 1 < max_pages) ? row[1] : -1;
-        if (2 * ji + 1 >= n_pages) p1 = -1;
+        const bool has_second = 2 * ji + 1 < n_pages;
         if (p0 < 0 || p0 >= num_pages) { raise_status(status, DSA_STATUS_BAD_PAGE); p0 = 0; }
-        if (p1 >= num_pages) { raise_status(status, DSA_STATUS_BAD_PAGE); p1 = 0; }
+        if (!has_second) {
+          p1 = -1;
+        } else if (p1 < 0 || p1 >= num_pages) {
+          raise_status(status, DSA_STATUS_BAD_PAGE);
+          p1 = 0;
+        }
         const int n = min(32, w1 - w);
         for (int i = 0; i < n; ++i) {
           const int tb = __shfl_sync(0xffffffffu, bi, i);
@@ -272,9 +287,46 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
         key_max = 0u;
         key_min_inv = 0u;
       };
+      // kHist: all four warps have counted the request's scores -> add the counts to its histogram
+      // in global memory and clear them (bounded group barrier before and after)
+      uint32_t gphase = 0;
+      auto group_sync = [&]() -> bool {
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(smem_u32(&sh.group));
+        const bool ok = ptx::mbar_wait(smem_u32(&sh.group), gphase);
+        gphase ^= 1u;
+        if (!ok) {
+          sh.abort_flag = 1;
+          raise_status(status, DSA_STATUS_WAIT_TIMEOUT);
+        }
+        return ok;
+      };
+      auto flush_hist = [&](int req) -> bool {
+        if (!group_sync()) return false;
+        const int et = (warp - 2) * 32 + lane;
+        uint32_t* g = ghist + (size_t)req * kFusedBins;
+        uint4* h4 = reinterpret_cast<uint4*>(sh.hist);
+#pragma unroll
+        for (int v = 0; v < kFusedBins / 4 / 128; ++v) {
+          const int q = v * 128 + et;
+          const uint4 cnt = h4[q];
+          if (cnt.x | cnt.y | cnt.z | cnt.w) {
+            if (cnt.x) atomicAdd(g + 4 * q, cnt.x);
+            if (cnt.y) atomicAdd(g + 4 * q + 1, cnt.y);
+            if (cnt.z) atomicAdd(g + 4 * q + 2, cnt.z);
+            if (cnt.w) atomicAdd(g + 4 * q + 3, cnt.w);
+            h4[q] = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+        return group_sync();
+      };
+      bool alive = true;
       for (int w = w0; w < w1; ++w) {
         if (w >= next_change) {
-          if (w > w0) flush_minmax(b);
+          if (w > w0) {
+            if (kHist) { if (!flush_hist(b)) { alive = false; break; } }
+            else flush_minmax(b);
+          }
           while (sh.prefix[b + 1] <= w) ++b;
           next_change = sh.prefix[b + 1];
           first_tile = sh.prefix[b];
@@ -313,7 +365,9 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
         const int t = (w - first_tile) * kTcTile + rowi;
         const float val = ((part[0] + part[1]) + (part[2] + part[3])) * sc;
         if (t < len) scores[(size_t)b * score_stride + t] = val;
-        if (minmax != nullptr) {
+        if (kHist) {
+          if (t < len) atomicAdd(&sh.hist[float_to_ordered(fmaxf(val, kScoreFloor)) >> 20], 1u);
+        } else if (minmax != nullptr) {
           const uint32_t key = t < len ? float_to_ordered(fmaxf(val, kScoreFloor)) : 0u;
           key_max = max(key_max, __reduce_max_sync(0xffffffffu, key));
           key_min_inv = max(key_min_inv, __reduce_max_sync(0xffffffffu, t < len ? ~key : 0u));
@@ -321,7 +375,8 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
         if (++stage == kTcStages) { stage = 0; phase ^= 1; }
         if (++acc == kTcAcc) { acc = 0; aphase ^= 1; }
       }
-      flush_minmax(b);
+      if (kHist) { if (alive) flush_hist(b); }
+      else flush_minmax(b);
     }
   }
 #undef DSA_WAIT
@@ -347,15 +402,18 @@ cudaError_t launch_indexer_score_tc(const void* q_fp8, const void* k_cache, cons
                                     const int32_t* seq_lens, const int32_t* block_table,
                                     int64_t bt_stride, float* scores, int64_t score_stride,
                                     int batch, int num_pages, int max_pages, int skip_short,
-                                    uint32_t* minmax, int32_t* status, cudaStream_t stream) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(indexer_score_tc_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)kTcDynBytes);
+                                    uint32_t* minmax, uint32_t* ghist, int32_t* status,
+                                    cudaStream_t stream) {
+  static std::atomic<uint64_t> smem_opted_a{0}, smem_opted_b{0};
+  {
+    cudaError_t e = opt_in_dynamic_smem(reinterpret_cast<const void*>(indexer_score_tc_kernel<false>),
+                                        kTcDynBytes, smem_opted_a);
+    if (e == cudaSuccess)
+      e = opt_in_dynamic_smem(reinterpret_cast<const void*>(indexer_score_tc_kernel<true>),
+                              kTcDynBytes, smem_opted_b);
     if (e != cudaSuccess) return e;
-    attr_set = true;
   }
+  if (ghist != nullptr && batch > kFusedMaxBatch) return cudaErrorInvalidValue;
   CUtensorMap tmap_k;
   if (!make_rows128_map(&tmap_k, k_cache, (uint64_t)num_pages * 66)) return cudaErrorInvalidValue;
   for (int b0 = 0; b0 < batch; b0 += kTcMaxBatch) {
@@ -374,10 +432,11 @@ cudaError_t launch_indexer_score_tc(const void* q_fp8, const void* k_cache, cons
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(
-        &cfg, indexer_score_tc_kernel, tmap_k, tmap_q, static_cast<const uint8_t*>(k_cache),
-        weights + (size_t)b0 * kIdxHeads, seq_lens + b0, block_table + (size_t)b0 * bt_stride,
-        bt_stride, scores + (size_t)b0 * score_stride, score_stride, nb, num_pages, max_pages,
-        skip_short, minmax != nullptr ? minmax + 2 * (size_t)b0 : nullptr, status);
+        &cfg, ghist != nullptr ? indexer_score_tc_kernel<true> : indexer_score_tc_kernel<false>, tmap_k,
+        tmap_q, static_cast<const uint8_t*>(k_cache), weights + (size_t)b0 * kIdxHeads, seq_lens + b0,
+        block_table + (size_t)b0 * bt_stride, bt_stride, scores + (size_t)b0 * score_stride,
+        score_stride, nb, num_pages, max_pages, skip_short,
+        minmax != nullptr ? minmax + 2 * (size_t)b0 : nullptr, ghist, status);
     if (e != cudaSuccess) return e;
   }
   return cudaSuccess;

@@ -11,7 +11,7 @@
 namespace dsa {
 cudaError_t launch_indexer_score_tc(const void*, const void*, const float*, const int32_t*,
                                     const int32_t*, int64_t, float*, int64_t, int, int, int, int,
-                                    uint32_t*, int32_t*, cudaStream_t);
+                                    uint32_t*, uint32_t*, int32_t*, cudaStream_t);
 cudaError_t launch_topk_select(const float*, int64_t, const int32_t*, const int32_t*, int64_t,
                                int32_t*, int64_t, int, int, uint32_t*, int32_t*, cudaStream_t);
 }  // namespace dsa
@@ -70,7 +70,7 @@ extern "C" int dsa_indexer_topk_noalloc(const void* q_fp8, const void* k_cache, 
   // are never observed.
   cudaError_t e = dsa::launch_indexer_score_tc(q_fp8, k_cache, weights, seq_lens, block_table,
                                                block_table_stride, scores, stride, batch, num_pages,
-                                               max_pages, 1, nullptr, status_dev, s);
+                                               max_pages, 1, nullptr, nullptr, status_dev, s);
   if (e != cudaSuccess) return static_cast<int>(e);
   e = dsa::launch_topk_select(scores, stride, seq_lens, block_table, block_table_stride, topk_out,
                               topk_stride, batch, max_pages, nullptr, status_dev, s);

@@ -546,8 +546,11 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
 // Clusters of `csize` CTAs of this kernel that can be resident at once (a cluster needs all its
 // SMs inside one GPC, so this is less than SMs / csize for the larger sizes); queried once.
 static int mm_max_active_clusters(int csize) {
-  static int cached[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
-  if (cached[csize] == 0) {
+  static std::atomic<int> cache[kMaxDevices][9];   // per device: 0 = not asked yet, -1 = query failed
+  const int dev = current_device();
+  std::atomic<int> uncached{0};
+  std::atomic<int>& slot = (dev >= 0 && dev < kMaxDevices) ? cache[dev][csize] : uncached;
+  if (slot.load(std::memory_order_relaxed) == 0) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(csize * 64));
     cfg.blockDim = dim3(kMmThreads);
@@ -564,9 +567,10 @@ static int mm_max_active_clusters(int csize) {
       cudaGetLastError();
       n = -1;
     }
-    cached[csize] = n;
+    slot.store(n, std::memory_order_relaxed);
   }
-  return cached[csize] > 0 ? cached[csize] : 0;
+  const int n = slot.load(std::memory_order_relaxed);
+  return n > 0 ? n : 0;
 }
 
 static int mm_cluster_size(int tokens, int tiles_per_token, int sms) {
@@ -584,15 +588,14 @@ cudaError_t launch_sparse_attn_mma(const void* q_nope, const void* q_pe, const v
                                    const void* kpe, const int32_t* indices, int64_t index_stride,
                                    float sm_scale, void* out, float* lse, int tokens, int topk,
                                    int64_t num_slots, void* ws, int32_t* status, cudaStream_t stream) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(sparse_attn_mma_kernel<false>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmDynBytes);
+  static std::atomic<uint64_t> smem_opted_a{0}, smem_opted_b{0};
+  {
+    cudaError_t e = opt_in_dynamic_smem(reinterpret_cast<const void*>(sparse_attn_mma_kernel<false>),
+                                        kMmDynBytes, smem_opted_a);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(sparse_attn_mma_kernel<true>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMmDynBytes);
+      e = opt_in_dynamic_smem(reinterpret_cast<const void*>(sparse_attn_mma_kernel<true>), kMmDynBytes,
+                              smem_opted_b);
     if (e != cudaSuccess) return e;
-    attr_set = true;
   }
   static int cluster_ok = -1;
   if (cluster_ok < 0) {   // DSA_ATT_CLUSTER=0 forces the contiguous-range split (for A/B timing)

@@ -648,12 +648,11 @@ cudaError_t launch_sparse_attn_tc(const void* q_nope, const void* q_pe, const vo
                                   const void* kpe, const int32_t* indices, int64_t index_stride,
                                   float sm_scale, void* out, float* lse, int tokens, int topk,
                                   int64_t num_slots, void* ws, int32_t* status, cudaStream_t stream) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(sparse_attn_tc_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kAtDynBytes);
+  static std::atomic<uint64_t> smem_opted{0};
+  {
+    cudaError_t e = opt_in_dynamic_smem(reinterpret_cast<const void*>(sparse_attn_tc_kernel), kAtDynBytes,
+                                        smem_opted);
     if (e != cudaSuccess) return e;
-    attr_set = true;
   }
   AtPlan plan = at_make_plan(tokens, topk, sm_count());
   sparse_attn_tc_kernel<<<plan.grid, kAtThreads, kAtDynBytes, stream>>>(

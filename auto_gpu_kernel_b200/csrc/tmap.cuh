@@ -7,6 +7,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdlib>
 
 namespace dsa {
@@ -56,18 +57,45 @@ inline int pdl_enabled() {
   return on;
 }
 
-inline int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
-      cudaGetLastError();
-      n = 0;
-      return 148;  // no device visible (host-only tooling): plan for a B200
-    }
+constexpr int kMaxDevices = 64;
+
+inline int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
   }
+  return dev;
+}
+
+// SM count of the CURRENT device (one process may drive several GPUs; cached per device).
+inline int sm_count() {
+  static std::atomic<int> cached[kMaxDevices];
+  const int dev = current_device();
+  if (dev < 0) return 148;  // no device visible (host-only tooling): plan for a B200
+  if (dev < kMaxDevices) {
+    const int n = cached[dev].load(std::memory_order_relaxed);
+    if (n > 0) return n;
+  }
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    return 148;
+  }
+  if (dev < kMaxDevices) cached[dev].store(n, std::memory_order_relaxed);
   return n;
+}
+
+// Opt a kernel in to more than 48 KB of dynamic shared memory.  Function attributes belong to the
+// current device's context, so this is remembered per device (`done` is one word per call site:
+// bit d = set on device d); devices beyond the mask get the attribute on every launch.
+inline cudaError_t opt_in_dynamic_smem(const void* kernel, size_t bytes, std::atomic<uint64_t>& done) {
+  const int dev = current_device();
+  const bool tracked = dev >= 0 && dev < 64;
+  if (tracked && ((done.load(std::memory_order_acquire) >> dev) & 1ull)) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess && tracked) done.fetch_or(1ull << dev, std::memory_order_release);
+  return e;
 }
 
 }  // namespace dsa

@@ -127,6 +127,10 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   };
 
   if (len <= kTopK) {  // every token is selected: no scores needed (uniform over the cluster)
+    // The output row may still be read by the kernel before us in the stream (the previous step's
+    // attention, when no scorer runs in between): no global write before the dependency wait.
+    ptx::launch_dependents();
+    ptx::grid_dependency_wait();
     for (int i = crank * kSelThreads + tid; i < kTopK; i += csize * kSelThreads)
       out_row[i] = i < len ? table[i >> 6] * kPage + (i & 63) : -1;
     if (minmax != nullptr && crank == 0 && tid == 0) { minmax[2 * b] = 0u; minmax[2 * b + 1] = 0u; }
@@ -278,7 +282,10 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   // inside the bin: first the lower-ranked CTAs' share (low[k]), then this CTA's in arrival order.
   auto candidate = [&](int i) {
     const uint32_t c = atomicAdd(&sh.cnt_cand, 1u);
-    if (c < (uint32_t)kSelCandCap) { sh.cand_key[c] = float_to_ordered(__ldg(row + i)); sh.cand_idx[c] = i; }
+    if (c < (uint32_t)kSelCandCap) {   // NaN and -inf rank as kSelFloor here as in the bins
+      sh.cand_key[c] = float_to_ordered(fmaxf(__ldg(row + i), kSelFloor));
+      sh.cand_idx[c] = i;
+    }
   };
   for (int i = tid * 4; i < n4s; i += kSelThreads * 4) {
     const int4 bq = *reinterpret_cast<const int4*>(bin_s + i);
@@ -349,7 +356,7 @@ topk_select_kernel(const float* __restrict__ scores, int64_t score_stride,
   //      boundary bin ----------------------------------------------------------------------------
   if (crank == 0) {
     auto key_in_edge = [&](int i, uint32_t& key) -> bool {
-      const float v = __ldg(row + i);
+      const float v = fmaxf(__ldg(row + i), kSelFloor);   // NaN and -inf rank as kSelFloor
       key = float_to_ordered(v);
       return bin_of(v) == edge;
     };
@@ -435,13 +442,11 @@ cudaError_t launch_topk_select(const float* scores, int64_t score_stride, const 
                                const int32_t* block_table, int64_t bt_stride, int32_t* out,
                                int64_t out_stride, int batch, int max_pages, uint32_t* minmax,
                                int32_t* status, cudaStream_t stream) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(topk_select_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)(sizeof(float) * kSelRowCap));
+  static std::atomic<uint64_t> smem_opted{0};
+  {
+    cudaError_t e = opt_in_dynamic_smem(reinterpret_cast<const void*>(topk_select_kernel),
+                                        sizeof(float) * kSelRowCap, smem_opted);
     if (e != cudaSuccess) return e;
-    attr_set = true;
   }
   const int csize = select_cluster_size(batch, max_pages * kPage);
   const int seg_max = (((max_pages * kPage + csize - 1) / csize) + 3) & ~3;

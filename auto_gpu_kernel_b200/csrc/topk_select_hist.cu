@@ -1,0 +1,393 @@
+// Top-2048 selection that starts from a finished histogram (reference: torch.topk + page remap +
+// -1 padding, indexer_baseline.py:60, :82-90).
+//
+// The scorer (indexer_score_tc_kernel<true>) has already counted every score of a request into
+// 4096 bins over the top 12 bits of its order-preserving key.  What is left is a short chain:
+//   (1) boundary bin: one read of the 16 KB histogram and one block scan (every CTA of the request's
+//       cluster does it for itself, while its slice of the score row is on its way into shared memory);
+//   (2) one counting sweep over the staged slice (elements above the boundary bin, elements inside
+//       it), one block scan, one exchange of the CTAs' totals through distributed shared memory:
+//       every selected element then has its place in the output row without any atomic;
+//   (3) the writing sweep; elements of the boundary bin go (key, position) into the first CTA's
+//       candidate list;
+//   (4) the first CTA picks the missing elements among the candidates exactly, by (key, lower
+//       position first), eight bits of the 52-bit composite per pass (normally one or two passes).
+// A boundary bin with more than 2048 elements (flat rows, mass ties) falls back to a radix descent
+// over the row.  One cluster of 1, 2 or 4 CTAs of 1024 threads per request; nothing waits on
+// another CTA outside cluster barriers.
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+#include "tmap.cuh"
+
+namespace dsa {
+
+namespace cg = cooperative_groups;
+
+constexpr int kShThreads = 1024;
+constexpr int kShRowCap = 45056;        // scores staged in dynamic shared memory (176 KB)
+constexpr int kShCandCap = 2048;
+constexpr int kShTableCap = 2048;       // block_table entries staged in shared memory (128K tokens)
+constexpr int kShBinShift = 20;         // bin = top 12 bits of the ordered key
+
+struct ShShared {
+  uint32_t cand_key[kShCandCap];
+  uint32_t cand_idx[kShCandCap];
+  int32_t table[kShTableCap];
+  uint32_t sub[256];
+  uint32_t warp_sums[32];
+  uint32_t edge, above, in_edge, digit, dabove, dcount, emit_cnt, carry;
+  uint32_t peer_sel[4], peer_cnd[4];    // written by the peers
+};
+
+__device__ __forceinline__ uint32_t sh_key(float v) { return float_to_ordered(fmaxf(v, kScoreFloor)); }
+
+// Exclusive prefix sum over the CTA in thread order (three block barriers).
+__device__ __forceinline__ uint32_t sh_block_excl_scan(uint32_t v, uint32_t* warp_sums, uint32_t* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t n = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += n;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t w = warp_sums[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t n = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += n;
+    }
+    warp_sums[lane] = w;
+  }
+  __syncthreads();
+  const uint32_t before = warp > 0 ? warp_sums[warp - 1] : 0u;
+  if (total != nullptr) *total = warp_sums[31];
+  __syncthreads();  // warp_sums may be reused by the caller
+  return before + incl - v;
+}
+
+// Digit d of sh.sub[0..255], scanned from the top, with count(> d) < want <= count(>= d); done by
+// the first warp (eight digits per lane).  Results in sh.digit / dabove / dcount.
+__device__ __forceinline__ void sh_pick_digit(ShShared& sh, uint32_t want) {
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x < 32) {
+    uint32_t c[8], mine = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { c[k] = sh.sub[255 - 8 * lane - k]; mine += c[k]; }
+    uint32_t incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    uint32_t run = incl - mine;
+    if (run < want && want <= incl) {
+      bool found = false;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if (!found && run + c[k] >= want) {
+          sh.digit = 255 - 8 * lane - k; sh.dabove = run; sh.dcount = c[k];
+          found = true;
+        }
+        run += c[k];
+      }
+    }
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kShThreads, 1)
+topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
+                        const int32_t* __restrict__ seq_lens, const int32_t* __restrict__ block_table,
+                        int64_t bt_stride, int32_t* __restrict__ out, int64_t out_stride,
+                        int max_pages, uint32_t* __restrict__ ghist, int32_t* status) {
+  extern __shared__ float row_s[];
+  __shared__ ShShared sh;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int csize = (int)cluster.num_blocks();   // CTAs per request: 1, 2 or 4
+  const int crank = (int)cluster.block_rank();
+
+  const int b = blockIdx.x / csize;
+  const int tid = threadIdx.x, lane = tid & 31;
+  int len = seq_lens[b];
+  len = max(0, min(len, max_pages * kPage));
+  int32_t* out_row = out + (size_t)b * out_stride;
+  const int32_t* table = block_table + (size_t)b * bt_stride;
+  const float* row = scores + (size_t)b * score_stride;
+  const int n_pages = (len + kPage - 1) / kPage;
+  const bool table_staged = n_pages <= kShTableCap;
+  auto slot_of = [&](int i) -> int32_t {
+    return (table_staged ? sh.table[i >> 6] : __ldg(table + (i >> 6))) * kPage + (i & 63);
+  };
+  // inputs of the caller only: safe before the dependency wait
+  if (table_staged) {
+    for (int i = tid; i < n_pages; i += kShThreads) sh.table[i] = table[i];
+  }
+  if (tid == 0) { sh.in_edge = 0xFFFFFFFFu; sh.edge = 0; sh.above = 0; sh.emit_cnt = 0; }
+  // The successor (the attention kernel) reads nothing before its own wait; nothing is written
+  // here before ours: the output row may still be read by the kernel before us in the stream.
+  ptx::launch_dependents();
+  ptx::grid_dependency_wait();
+
+  if (len <= kTopK) {  // every token is selected: no scores, no histogram (uniform over the cluster)
+    __syncthreads();
+    for (int i = crank * kShThreads + tid; i < kTopK; i += csize * kShThreads)
+      out_row[i] = i < len ? slot_of(i) : -1;
+    return;
+  }
+
+  // this CTA's segment [seg_lo, seg_hi) of the row (multiples of 4 keep the 16-byte loads aligned)
+  const int seg = ((len + csize - 1) / csize + 3) & ~3;
+  const int seg_lo = min(len, crank * seg), seg_hi = min(len, seg_lo + seg);
+  const int seg_len = seg_hi - seg_lo;
+  const bool staged = seg <= kShRowCap;
+  const bool vec = (reinterpret_cast<uintptr_t>(row) & 15u) == 0;
+
+  // ---- (1) histogram -> boundary bin, while the slice travels into shared memory ----------------
+  // thread t owns bins 4095-4t .. 4092-4t (one 16-byte load), so thread order is rank order
+  uint4* g4 = reinterpret_cast<uint4*>(ghist + (size_t)b * kFusedBins);
+  const uint4 h = __ldcg(g4 + (kFusedBins / 4 - 1 - tid));
+  if (staged) {
+    const int n4 = vec ? (seg_len & ~3) : 0;
+    for (int i = tid * 4; i < n4; i += kShThreads * 4)
+      *reinterpret_cast<float4*>(row_s + i) = __ldcg(reinterpret_cast<const float4*>(row + seg_lo + i));
+    for (int i = n4 + tid; i < seg_len; i += kShThreads) row_s[i] = __ldcg(row + seg_lo + i);
+  }
+  {
+    const uint32_t mine = h.x + h.y + h.z + h.w;
+    const uint32_t excl = sh_block_excl_scan(mine, sh.warp_sums, nullptr);
+    if (excl < (uint32_t)kTopK && (uint32_t)kTopK <= excl + mine) {
+      const uint32_t c[4] = {h.w, h.z, h.y, h.x};   // highest bin first
+      uint32_t run = excl;
+      bool found = false;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (!found && run + c[k] >= (uint32_t)kTopK) {
+          sh.edge = (uint32_t)(kFusedBins - 1 - 4 * tid - k); sh.above = run; sh.in_edge = c[k];
+          found = true;
+        }
+        run += c[k];
+      }
+    }
+  }
+  __syncthreads();   // boundary known; staged slice complete
+  const uint32_t edge = sh.edge, above = sh.above, in_edge = sh.in_edge;
+  if (in_edge == 0xFFFFFFFFu) {   // the histogram does not hold this row (workspace not zeroed?)
+    if (tid == 0 && crank == 0) raise_status(status, DSA_STATUS_TOPK_COUNT);
+    return;                       // uniform over the cluster: every CTA read the same histogram
+  }
+  const uint32_t need = (uint32_t)kTopK - above;   // elements wanted from the boundary bin (>= 1)
+  const bool few = in_edge <= (uint32_t)kShCandCap;
+  auto key_at = [&](int i) -> uint32_t { return sh_key(staged ? row_s[i - seg_lo] : __ldcg(row + i)); };
+
+  // ---- (2) counting sweep --------------------------------------------------------------------------
+  // A thread owns four consecutive elements per step; both sweeps walk them in the same order.
+  uint32_t n_sel = 0, n_cnd = 0;
+  const int n4s = staged ? (seg_len & ~3) : 0;
+  for (int i = tid * 4; i < n4s; i += kShThreads * 4) {
+    const float4 q = *reinterpret_cast<const float4*>(row_s + i);
+    const uint32_t b0 = sh_key(q.x) >> kShBinShift, b1 = sh_key(q.y) >> kShBinShift;
+    const uint32_t b2 = sh_key(q.z) >> kShBinShift, b3 = sh_key(q.w) >> kShBinShift;
+    n_sel += (b0 > edge) + (b1 > edge) + (b2 > edge) + (b3 > edge);
+    n_cnd += (b0 == edge) + (b1 == edge) + (b2 == edge) + (b3 == edge);
+  }
+  for (int i = seg_lo + n4s + tid; i < seg_hi; i += kShThreads) {
+    const uint32_t bin = key_at(i) >> kShBinShift;
+    n_sel += bin > edge;
+    n_cnd += bin == edge;
+  }
+  uint32_t totals = 0;
+  const uint32_t excl = sh_block_excl_scan(n_sel | (n_cnd << 16), sh.warp_sums, &totals);
+  // (a CTA holds at most 45056 staged elements, a streamed slice counts below 65536 per field only
+  //  when it is shorter than that: longer streamed slices are rejected by the launcher)
+  if (tid < csize) {   // publish this CTA's totals in every CTA of the cluster
+    ShShared* peer = cluster.map_shared_rank(&sh, tid);
+    peer->peer_sel[crank] = totals & 0xFFFFu;
+    peer->peer_cnd[crank] = totals >> 16;
+  }
+  cluster.sync();
+  if (crank == 0 && tid < kFusedBins / 4) g4[tid] = make_uint4(0u, 0u, 0u, 0u);   // every CTA has read it
+  uint32_t sel_at = excl & 0xFFFFu, cnd_at = excl >> 16, nc = 0, sel_all = 0;
+  for (int r = 0; r < csize; ++r) {
+    if (r < crank) { sel_at += sh.peer_sel[r]; cnd_at += sh.peer_cnd[r]; }
+    nc += sh.peer_cnd[r];
+    sel_all += sh.peer_sel[r];
+  }
+  if (crank == 0 && tid == 0 && (sel_all != above || nc != in_edge)) raise_status(status, DSA_STATUS_TOPK_COUNT);
+
+  // ---- (3) writing sweep: selected elements to their places, boundary bin to the candidate list --
+  ShShared* first = cluster.map_shared_rank(&sh, 0);
+  auto place = [&](int i, uint32_t key) {
+    const uint32_t bin = key >> kShBinShift;
+    if (bin > edge) {
+      if (sel_at < (uint32_t)kTopK) out_row[sel_at] = slot_of(i);
+      ++sel_at;
+    } else if (bin == edge) {
+      if (few && cnd_at < (uint32_t)kShCandCap) { first->cand_key[cnd_at] = key; first->cand_idx[cnd_at] = (uint32_t)i; }
+      ++cnd_at;
+    }
+  };
+  for (int i = tid * 4; i < n4s; i += kShThreads * 4) {
+    const float4 q = *reinterpret_cast<const float4*>(row_s + i);
+    place(seg_lo + i, sh_key(q.x));
+    place(seg_lo + i + 1, sh_key(q.y));
+    place(seg_lo + i + 2, sh_key(q.z));
+    place(seg_lo + i + 3, sh_key(q.w));
+  }
+  for (int i = seg_lo + n4s + tid; i < seg_hi; i += kShThreads) place(i, key_at(i));
+  cluster.sync();   // candidates are in the first CTA's shared memory; the peers are done
+  if (crank != 0) return;
+
+  // ---- (4) the first CTA chooses `need` elements of the boundary bin -----------------------------
+  auto emit = [&](int i) {
+    const uint32_t p = above + atomicAdd(&sh.emit_cnt, 1u);
+    if (p < (uint32_t)kTopK) out_row[p] = slot_of(i);
+  };
+  if (few) {
+    nc = min(nc, (uint32_t)kShCandCap);
+    if (need >= nc) {
+      for (uint32_t j = tid; j < nc; j += kShThreads) emit((int)sh.cand_idx[j]);
+    } else {
+      // composite = low 20 key bits, then ~position (the lower position wins a tie)
+      auto composite = [&](uint32_t j) -> uint64_t {
+        return ((uint64_t)(sh.cand_key[j] & 0xFFFFFu) << 32) | (uint64_t)(~sh.cand_idx[j]);
+      };
+      uint64_t pfx = 0, msk = 0;
+      uint32_t want = need;
+#pragma unroll 1
+      for (int pass = 0; pass < 7; ++pass) {
+        const int shift = pass < 6 ? 44 - 8 * pass : 0;
+        if (tid < 256) sh.sub[tid] = 0;
+        if (tid == 0) sh.dcount = 0xFFFFFFFFu;
+        __syncthreads();
+        for (uint32_t j = tid; j < nc; j += kShThreads) {
+          const uint64_t cj = composite(j);
+          if ((cj & msk) == pfx) atomicAdd(&sh.sub[(uint32_t)(cj >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        sh_pick_digit(sh, want);
+        const uint32_t d = sh.digit, da = sh.dabove, dc = sh.dcount;
+        if (dc == 0xFFFFFFFFu) {   // cannot happen with consistent counts
+          if (tid == 0) raise_status(status, DSA_STATUS_TOPK_COUNT);
+          break;
+        }
+        const bool take_all = dc == want - da;
+        for (uint32_t j = tid; j < nc; j += kShThreads) {
+          const uint64_t cj = composite(j);
+          if ((cj & msk) != pfx) continue;
+          const uint32_t dg = (uint32_t)(cj >> shift) & 255u;
+          if (dg > d || (take_all && dg == d)) emit((int)sh.cand_idx[j]);
+        }
+        if (take_all) break;
+        want -= da;
+        pfx |= (uint64_t)d << shift;
+        msk |= 255ull << shift;
+        __syncthreads();   // everyone has read the digit before it is reset
+      }
+    }
+  } else {
+    // radix descent over the whole row (L2) for the exact threshold key inside the boundary bin,
+    // then the ties in position order
+    uint32_t pfx = edge << kShBinShift, msk = 0xFFFu << kShBinShift, want = need;
+#pragma unroll 1
+    for (int pass = 0; pass < 3; ++pass) {
+      const int shift = pass == 0 ? 12 : (pass == 1 ? 4 : 0);
+      const uint32_t dmask = pass == 2 ? 15u : 255u;
+      if (tid < 256) sh.sub[tid] = 0;
+      if (tid == 0) sh.dcount = 0xFFFFFFFFu;
+      __syncthreads();
+      for (int i = tid; i < len; i += kShThreads) {
+        const uint32_t k = sh_key(__ldcg(row + i));
+        if ((k & msk) == pfx) atomicAdd(&sh.sub[(k >> shift) & dmask], 1u);
+      }
+      __syncthreads();
+      sh_pick_digit(sh, want);
+      if (sh.dcount == 0xFFFFFFFFu) {
+        if (tid == 0) raise_status(status, DSA_STATUS_TOPK_COUNT);
+        break;
+      }
+      want -= sh.dabove;
+      pfx |= sh.digit << shift;
+      msk |= dmask << shift;
+      __syncthreads();
+    }
+    const uint32_t thresh = pfx;   // key of the last selected element; `want` copies of it are taken
+    for (int i = tid; i < len; i += kShThreads) {
+      const uint32_t k = sh_key(__ldcg(row + i));
+      if ((k >> kShBinShift) == edge && k > thresh) emit(i);
+    }
+    uint32_t running = 0;
+    for (int base = 0; base < len && running < want; base += kShThreads * 4) {
+      const int i = base + tid * 4;
+      uint32_t eq = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (i + e < len && sh_key(__ldcg(row + i + e)) == thresh) eq |= 1u << e;
+      uint32_t block_total = 0;
+      uint32_t rank = running + sh_block_excl_scan((uint32_t)__popc(eq), sh.warp_sums, &block_total);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if ((eq >> e) & 1u) {
+          if (rank < want) emit(i + e);
+          ++rank;
+        }
+      }
+      running += block_total;
+    }
+  }
+  __syncthreads();
+  if (tid == 0 && sh.emit_cnt != need) raise_status(status, DSA_STATUS_TOPK_COUNT);
+}
+
+// CTAs per request: as many as fit in one wave, more when a CTA's share of the longest possible
+// row would not fit the staging buffer (a staged slice is read from L2 once).
+static int sh_cluster_size(int batch, int max_len) {
+  const int sms = sm_count();
+  int c = batch * 4 <= sms ? 4 : (batch * 2 <= sms ? 2 : 1);
+  while (c < 4 && (max_len + c - 1) / c > kShRowCap) c *= 2;
+  return c;
+}
+
+// Rows whose slice per CTA could not be counted in 16 bits when streamed are left to the
+// histogram-free selection kernel.
+bool topk_select_hist_supports(int batch, int max_pages) {
+  const int c = sh_cluster_size(batch, max_pages * kPage);
+  const int64_t seg = ((int64_t)max_pages * kPage + c - 1) / c;
+  return batch <= kFusedMaxBatch && (seg <= kShRowCap || seg < 65536);
+}
+
+cudaError_t launch_topk_select_hist(const float* scores, int64_t score_stride, const int32_t* seq_lens,
+                                    const int32_t* block_table, int64_t bt_stride, int32_t* out,
+                                    int64_t out_stride, int batch, int max_pages, uint32_t* ghist,
+                                    int32_t* status, cudaStream_t stream) {
+  static std::atomic<uint64_t> smem_opted{0};
+  {
+    cudaError_t e = opt_in_dynamic_smem(reinterpret_cast<const void*>(topk_select_hist_kernel),
+                                        sizeof(float) * kShRowCap, smem_opted);
+    if (e != cudaSuccess) return e;
+  }
+  const int csize = sh_cluster_size(batch, max_pages * kPage);
+  const int seg_max = (((max_pages * kPage + csize - 1) / csize) + 3) & ~3;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(batch * csize));
+  cfg.blockDim = dim3(kShThreads);
+  cfg.dynamicSmemBytes = sizeof(float) * (size_t)min(kShRowCap, max(seg_max, 4));
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = csize;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled();
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return cudaLaunchKernelEx(&cfg, topk_select_hist_kernel, scores, score_stride, seq_lens,
+                            block_table, bt_stride, out, out_stride, max_pages, ghist, status);
+}
+
+}  // namespace dsa

@@ -65,3 +65,45 @@ def assert_attention_close(out, lse, ref_out, ref_lse, label=""):
     err = (out[keep] - ref_out[keep]).abs()
     bound = ATT_ATOL + ATT_RTOL * ref_out[keep].abs()
     assert (err <= bound).all(), f"{label}: output max err {err.max()}"
+
+
+def indexer_inputs_from_scores(rows, lens, seed=0, device="cpu"):
+    """Indexer inputs whose score rows are EXACTLY the given fp32 rows (any sign, +-0, inf, NaN).
+
+    Two heads carry everything: q[0] = +e0, q[1] = -e0, w[0] = +1, w[1] = -1, all else zero; token t
+    holds the key sign(x_t) * e0 with the per-token scale |x_t|.  Then (reference order, scale
+    inside the key: indexer_baseline.py:36,75-80) relu(x)*1 + relu(-x)*(-1) = x, and (kernel order,
+    scale after the head sum) |x| * (+1 or -1) = x, both without rounding."""
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    lens = [int(n) for n in lens]
+    batch = len(lens)
+    need = [(n + 63) // 64 for n in lens]
+    total = max(sum(need), 1)
+    max_pages = max(1, max(need))
+    perm = torch.randperm(total, generator=gen).to(torch.int32)
+    table = torch.zeros(batch, max_pages, dtype=torch.int32)
+    raw = torch.zeros(total, wl.PAGE_BYTES, dtype=torch.uint8)
+    data = raw[:, : 64 * 128].view(total, 64, 128)
+    scales = torch.zeros(total, 64, dtype=torch.float32)
+    plus_one = int(torch.tensor([1.0]).to(torch.float8_e4m3fn).view(torch.uint8))
+    minus_one = int(torch.tensor([-1.0]).to(torch.float8_e4m3fn).view(torch.uint8))
+    at = 0
+    for b, n in enumerate(need):
+        pages = perm[at:at + n].long()
+        table[b, :n] = perm[at:at + n]
+        at += n
+        x = torch.zeros(n * 64, dtype=torch.float32)
+        x[: lens[b]] = rows[b][: lens[b]].float()
+        negative = torch.signbit(x)
+        data[pages, :, 0] = torch.where(negative, minus_one, plus_one).to(torch.uint8).view(n, 64)
+        scales[pages] = x.abs().view(n, 64)
+    raw[:, 64 * 128:] = scales.view(torch.uint8).reshape(total, -1)
+    cache = raw.view(torch.int8).reshape(total, 64, 1, 132)
+    q = torch.zeros(batch, 64, 128)
+    q[:, 0, 0] = 1.0
+    q[:, 1, 0] = -1.0
+    w = torch.zeros(batch, 64)
+    w[:, 0] = 1.0
+    w[:, 1] = -1.0
+    inp = wl.IndexerInputs(q.to(torch.float8_e4m3fn), cache, w, torch.tensor(lens, dtype=torch.int32), table)
+    return inp.to(device)

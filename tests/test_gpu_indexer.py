@@ -164,10 +164,12 @@ def test_prefill_scorer_ragged_lengths(cuda):
 
 
 @pytest.mark.parametrize("junk", ["random", "ones", "nan", "tiny_range"])
-def test_foreign_minmax_words_cost_speed_not_correctness(cuda, junk):
-    """The scorer leaves each row's min / max in the workspace for the selection.  Whatever those
-    words hold when a call starts (an aborted call, a caller that did not zero the workspace), the
-    selected set stays exact: the bins are clamped and monotone for any [lo, hi]."""
+def test_foreign_minmax_words_cost_speed_not_correctness(cuda, junk, monkeypatch):
+    """Two-kernel path (DSA_INDEXER_PATH=minmax; also taken by batches beyond 1024 requests): the scorer leaves
+    each row's min / max in the workspace for the selection.  Whatever those words hold when a
+    call starts (an aborted call, a caller that did not zero the workspace), the selected set
+    stays exact: the bins are clamped and monotone for any [lo, hi]."""
+    monkeypatch.setenv("DSA_INDEXER_PATH", "minmax")
     lens = [3000, 2049, 40000, 9000]
     inp = wl.make_indexer_inputs(lens, seed=17, device=cuda)
     rows = [r.cpu() for r in oracle.indexer_scores(*inp.args())]
