@@ -48,31 +48,59 @@ def decode_block_local(idx_args, q_nope, q_pe, ckv_cache, kpe_cache, sm_scale, t
     return output, lse
 
 
-def gather_indices(local_indices: torch.Tensor, counts, group=None) -> torch.Tensor:
-    """All-gather of the per-rank index rows into the full [B, 2048] tensor (rank order).
+class HeadShardedPlan:
+    """Buffers of the head-sharded layout, allocated once: the rank's own index rows are written by
+    the indexer straight into its slot of the gathered tensor's source buffer, and every step's
+    all-gather lands in the same pre-allocated [world * most, 2048] tensor -- no allocation, copy
+    or concatenation per step.
 
-    `counts[r]` is the number of requests of rank r.  Equal counts use one
-    all_gather_into_tensor; ragged counts pad to the largest shard first."""
+    counts[r] = requests of rank r.  With equal counts (the usual case: B divisible by the world
+    size) `all_rows` is the gathered tensor itself; with ragged counts every shard is padded to
+    the largest one with rows of -1 and `all_rows` is a compacted copy made after the gather."""
+
+    def __init__(self, counts, rank, device, group=None, width=TOPK):
+        self.counts = [int(c) for c in counts]
+        self.rank, self.group, self.world = rank, group, len(self.counts)
+        self.most = max(self.counts)
+        self.equal = all(c == self.most for c in self.counts)
+        self.padded = torch.full((self.most, width), -1, dtype=torch.int32, device=device)
+        self.local_rows = self.padded[: self.counts[rank]]
+        if self.world == 1:
+            self.gathered = self.padded
+            self.all_rows = self.local_rows
+        else:
+            self.gathered = torch.empty(self.world * self.most, width, dtype=torch.int32, device=device)
+            self.all_rows = self.gathered if self.equal else torch.empty(sum(self.counts), width,
+                                                                        dtype=torch.int32, device=device)
+
+    def gather(self):
+        """All-gather of the index rows (the one collective of the path); returns `all_rows`."""
+        if self.world == 1:
+            return self.all_rows
+        dist.all_gather_into_tensor(self.gathered, self.padded, group=self.group)
+        if not self.equal:
+            at = 0
+            for r, c in enumerate(self.counts):
+                self.all_rows[at:at + c].copy_(self.gathered[r * self.most: r * self.most + c])
+                at += c
+        return self.all_rows
+
+
+def gather_indices(local_indices: torch.Tensor, counts, group=None) -> torch.Tensor:
+    """All-gather of the per-rank index rows into the full [B, 2048] tensor (rank order), for
+    callers without a plan: allocates its result.  `counts[r]` = requests of rank r."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     if world == 1:
         return local_indices
-    width = local_indices.shape[1]
-    most = max(counts)
-    if local_indices.shape[0] != most:
-        pad = torch.full((most - local_indices.shape[0], width), -1, dtype=local_indices.dtype,
-                         device=local_indices.device)
-        local_indices = torch.cat([local_indices, pad], dim=0)
-    gathered = torch.empty(world * most, width, dtype=local_indices.dtype, device=local_indices.device)
-    dist.all_gather_into_tensor(gathered, local_indices.contiguous(), group=group)
-    if all(c == most for c in counts):
-        return gathered
-    rows = [gathered[r * most: r * most + counts[r]] for r in range(world)]
-    return torch.cat(rows, dim=0)
+    rank = dist.get_rank(group)
+    plan = HeadShardedPlan(counts, rank, local_indices.device, group, local_indices.shape[1])
+    plan.local_rows.copy_(local_indices)
+    return plan.gather()
 
 
 def decode_block_head_sharded(idx_args_local, counts, q_nope_heads, q_pe_heads, ckv_cache, kpe_cache,
                               sm_scale, output, lse, local_indices=None, group=None, indexer_fn=None,
-                              attention_fn=None):
+                              attention_fn=None, plan=None):
     """Head-sharded layout of the full 128-head block (128 heads = 8 ranks x 16).
 
     idx_args_local : indexer inputs of this rank's request shard (q, cache, weights, seq_lens,
@@ -81,15 +109,43 @@ def decode_block_head_sharded(idx_args_local, counts, q_nope_heads, q_pe_heads, 
     q_nope_heads   : [B, 16, 512] bf16, this rank's heads of ALL tokens; q_pe_heads likewise
     ckv/kpe caches : replicated, identical page numbering on every rank
     output, lse    : [B, 16, 512] bf16 / [B, 16] fp32 for this rank's heads
+    plan           : a HeadShardedPlan kept across steps (no per-step allocation); without one a
+                     plan is made for this call (and `local_indices`, if given, receives a copy
+                     of the rank's own rows)
     Returns the gathered [B, 2048] index tensor.
     """
     if indexer_fn is None or attention_fn is None:
         indexer_fn, attention_fn = _default_ops()
     rank = dist.get_rank(group) if dist.is_initialized() else 0
-    if local_indices is None:
-        local_indices = torch.empty(counts[rank], TOPK, dtype=torch.int32,
-                                    device=q_nope_heads.device)
-    indexer_fn(*idx_args_local, local_indices)
-    all_indices = gather_indices(local_indices, counts, group)
+    if plan is None:
+        plan = HeadShardedPlan(counts, rank, q_nope_heads.device, group)
+    indexer_fn(*idx_args_local, plan.local_rows)
+    all_indices = plan.gather()
+    if local_indices is not None:
+        local_indices.copy_(plan.local_rows)
     attention_fn(q_nope_heads, q_pe_heads, ckv_cache, kpe_cache, all_indices, sm_scale, output, lse)
     return all_indices
+
+
+def prefill_block_token_sharded(idx_args, q_nope, q_pe, ckv_cache, kpe_cache, sm_scale, rank, world,
+                                indexer_fn=None, attention_fn=None):
+    """Chunked prefill of ONE request with the chunk's query tokens sharded over the ranks (query
+    tokens are independent in both definitions, the key pages and ckv/kpe caches are replicated,
+    so there is no collective).  idx_args = (q [T,64,128], cache, weights [T,64], seq_lens [T],
+    block_table [1 or T, pages]) for the whole chunk; every rank runs its contiguous token range
+    (`shard_range`) and returns (range, topk_indices, output, lse) for it.  A block_table of one
+    row, or of T identical rows, is passed on with row stride 0 so that the shared-pages scorer
+    is used."""
+    if indexer_fn is None or attention_fn is None:
+        indexer_fn, attention_fn = _default_ops()
+    q, cache, weights, seq_lens, table = idx_args
+    mine = shard_range(q.shape[0], rank, world)
+    sel = slice(mine.start, mine.stop)
+    n = len(mine)
+    shared = table[:1].expand(n, -1)
+    topk = torch.empty(n, TOPK, dtype=torch.int32, device=q.device)
+    indexer_fn(q[sel].contiguous(), cache, weights[sel].contiguous(), seq_lens[sel].contiguous(), shared, topk)
+    out = torch.empty(n, q_nope.shape[1], q_nope.shape[2], dtype=q_nope.dtype, device=q.device)
+    lse = torch.empty(n, q_nope.shape[1], dtype=torch.float32, device=q.device)
+    attention_fn(q_nope[sel].contiguous(), q_pe[sel].contiguous(), ckv_cache, kpe_cache, topk, sm_scale, out, lse)
+    return mine, topk, out, lse

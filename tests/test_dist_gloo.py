@@ -86,3 +86,77 @@ def test_head_sharded_block_on_two_gloo_ranks(tmp_path, lens):
     result = tmp_path / "result.txt"
     mp.spawn(_worker, args=(2, _free_port(), lens, str(result)), nprocs=2, join=True)
     assert result.read_text() == "ok"
+
+
+def _prefill_worker(rank, world, port, result_path):
+    import dsa_oracle as oracle
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(2)
+        chunk = 7                                                     # not divisible by the world size
+        inp = wl.make_shared_prefix_indexer_inputs(prefix_len=2300, chunk_len=chunk, seed=9)
+        att = wl.make_attention_inputs([2400] * chunk, seed=9)       # queries and caches only
+        pages = inp.k_index_cache_fp8.shape[0]
+        ckv, kpe = att.ckv_cache[:pages], att.kpe_cache[:pages]
+        calls = []
+
+        def indexer_fn(q, cache, w, sl, bt, topk):
+            calls.append(bt.stride(0))
+            oracle.indexer_topk(q, cache, w, sl, bt.contiguous(), topk_indices=topk)
+
+        def attention_fn(qn, qp, c, k, ind, scale, o, l):
+            oracle.sparse_attention(qn, qp, c, k, ind, scale, output=o, lse=l)
+
+        mine, topk, out, lse = dsa_dist.prefill_block_token_sharded(
+            inp.args(), att.q_nope, att.q_pe, ckv, kpe, att.sm_scale, rank, world,
+            indexer_fn=indexer_fn, attention_fn=attention_fn)
+        want_idx = oracle.indexer_topk(*inp.args())
+        want_out, want_lse = oracle.sparse_attention(att.q_nope, att.q_pe, ckv, kpe, want_idx, att.sm_scale)
+        sel = slice(mine.start, mine.stop)
+        ok = bool(calls == [0] and torch.equal(topk, want_idx[sel]) and torch.equal(lse, want_lse[sel])
+                  and torch.equal(out.view(torch.int16), want_out[sel].view(torch.int16)))
+        # the shards of all ranks tile the chunk
+        spans = [None] * world
+        dist.all_gather_object(spans, (mine.start, mine.stop, ok))
+        if rank == 0:
+            tiled = [i for a, b, _ in spans for i in range(a, b)] == list(range(chunk))
+            Path(result_path).write_text("ok" if tiled and all(s[2] for s in spans) else f"mismatch {spans}")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_token_sharded_prefill_on_two_gloo_ranks(tmp_path):
+    result = tmp_path / "result.txt"
+    mp.spawn(_prefill_worker, args=(2, _free_port(), str(result)), nprocs=2, join=True)
+    assert result.read_text() == "ok"
+
+
+def _plan_worker(rank, world, port, result_path):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        ok = True
+        for counts in ([3, 3], [3, 2]):
+            plan = dsa_dist.HeadShardedPlan(counts, rank, torch.device("cpu"), width=8)
+            ptr = plan.all_rows.data_ptr()
+            for step in range(2):                                   # the same buffers every step
+                plan.local_rows.copy_(torch.full((counts[rank], 8), 10 * step + rank, dtype=torch.int32))
+                rows = plan.gather()
+                want = torch.cat([torch.full((c, 8), 10 * step + r, dtype=torch.int32)
+                                  for r, c in enumerate(counts)])
+                ok = ok and torch.equal(rows, want) and rows.data_ptr() == ptr
+        flags = [None] * world
+        dist.all_gather_object(flags, bool(ok))
+        if rank == 0:
+            Path(result_path).write_text("ok" if all(flags) else f"mismatch {flags}")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_head_sharded_plan_reuses_its_buffers(tmp_path):
+    result = tmp_path / "result.txt"
+    mp.spawn(_plan_worker, args=(2, _free_port(), str(result)), nprocs=2, join=True)
+    assert result.read_text() == "ok"

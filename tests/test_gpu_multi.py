@@ -69,3 +69,88 @@ def test_head_sharded_block_on_two_gpus(tmp_path):
     result = tmp_path / "result.txt"
     mp.spawn(_worker, args=(2, _free_port(), str(result)), nprocs=2, join=True)
     assert result.read_text() == "ok"
+
+
+def test_one_process_drives_two_gpus(cuda):
+    """The C ABI may be called for several devices from one process: kernel attributes (the
+    opt-in to large dynamic shared memory) and the SM count are kept per device, so the first
+    launch on cuda:1 after calls on cuda:0 works like the first launch on cuda:0."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    for p in (ROOT, ROOT / "oracle"):
+        if str(p) not in sys.path:
+            sys.path.insert(0, str(p))
+    import dsa_oracle as oracle
+    from auto_gpu_kernel_b200 import indexer, inputs as wl, sparse_attention, workspace
+    from helpers import assert_attention_close, assert_topk_matches
+    lens = [3000, 2100, 70, 5000]
+    results = []
+    for index in (0, 1, 0):
+        dev = torch.device("cuda", index)
+        block = wl.make_decode_block_inputs(lens, seed=12, device=dev)
+        idx = block.indexer
+        topk = indexer.run(*idx.args())
+        scores = indexer.scores(*idx.args(), variant=0)
+        out, lse = sparse_attention.run(block.q_nope, block.q_pe, block.ckv_cache, block.kpe_cache,
+                                        topk, block.sm_scale)
+        out_tc, lse_tc = sparse_attention.run(block.q_nope, block.q_pe, block.ckv_cache, block.kpe_cache,
+                                              topk, block.sm_scale, variant=2)
+        workspace.check_status(dev)
+        assert topk.device == dev and out.device == dev and scores.device == dev
+        assert_topk_matches(idx, topk, label=f"cuda:{index}")
+        ref_out, ref_lse = oracle.sparse_attention(block.q_nope.cpu(), block.q_pe.cpu(), block.ckv_cache.cpu(),
+                                                   block.kpe_cache.cpu(), topk.cpu(), block.sm_scale)
+        assert_attention_close(out, lse, ref_out, ref_lse, label=f"cuda:{index}")
+        assert_attention_close(out_tc, lse_tc, ref_out, ref_lse, label=f"cuda:{index} tcgen05")
+        results.append(torch.sort(topk.cpu(), dim=1).values)
+    assert torch.equal(results[0], results[1]) and torch.equal(results[0], results[2])
+
+
+def _prefill_worker(rank, world, port, result_path):
+    for p in (ROOT, ROOT / "oracle"):
+        if str(p) not in sys.path:
+            sys.path.insert(0, str(p))
+    import torch.distributed as dist
+    from auto_gpu_kernel_b200 import dist as dsa_dist, indexer, inputs as wl, sparse_attention, workspace
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        chunk = 150
+        inp = wl.make_shared_prefix_indexer_inputs(prefix_len=4000, chunk_len=chunk, seed=14, device=dev)
+        pages = inp.k_index_cache_fp8.shape[0]
+        gen = torch.Generator(device=dev).manual_seed(15)
+        ckv = torch.randn(pages, 64, 512, generator=gen, device=dev).to(torch.bfloat16)
+        kpe = torch.randn(pages, 64, 64, generator=gen, device=dev).to(torch.bfloat16)
+        qn = (torch.randn(chunk, 16, 512, generator=gen, device=dev) * 0.1).to(torch.bfloat16)
+        qp = (torch.randn(chunk, 16, 64, generator=gen, device=dev) * 0.1).to(torch.bfloat16)
+        mine, topk, out, lse = dsa_dist.prefill_block_token_sharded(inp.args(), qn, qp, ckv, kpe, 192 ** -0.5,
+                                                                    rank, world)
+        workspace.check_status(dev)
+        # the whole chunk on this GPU alone
+        shared = inp.block_table[:1].expand(chunk, -1)
+        want_idx = indexer.run(inp.q_index_fp8, inp.k_index_cache_fp8, inp.weights, inp.seq_lens, shared)
+        sel = slice(mine.start, mine.stop)
+        want_out, want_lse = sparse_attention.run(qn[sel].contiguous(), qp[sel].contiguous(), ckv, kpe, topk,
+                                                  192 ** -0.5)
+        ok = bool(torch.equal(torch.sort(topk, 1).values, torch.sort(want_idx[sel], 1).values)
+                  and torch.equal(out.view(torch.int16), want_out.view(torch.int16))
+                  and torch.equal(lse, want_lse))
+        flags = [None] * world
+        dist.all_gather_object(flags, ok)
+        if rank == 0:
+            Path(result_path).write_text("ok" if all(flags) else f"mismatch {flags}")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_token_sharded_prefill_on_two_gpus(tmp_path):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    result = tmp_path / "result.txt"
+    mp.spawn(_prefill_worker, args=(2, _free_port(), str(result)), nprocs=2, join=True)
+    assert result.read_text() == "ok"
