@@ -44,6 +44,7 @@ SIGNATURES = {
     "dsa_kv_cache_append": (_c_int, [_ptr, _c_i64, _ptr, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64,
                                      _ptr, _ptr]),
     "dsa_decode_step_host": (_c_int, [_ptr]),
+    "dsa_selftest_wait_expiry": (_c_int, [ctypes.c_uint64, _ptr, _ptr, _ptr]),
 }
 
 

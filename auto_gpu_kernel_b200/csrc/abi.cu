@@ -17,20 +17,12 @@ cudaError_t launch_topk_select_hist(const float*, int64_t, const int32_t*, const
 bool topk_select_hist_supports(int batch, int max_pages);
 cudaError_t launch_topk_select(const float*, int64_t, const int32_t*, const int32_t*, int64_t,
                                int32_t*, int64_t, int, int, uint32_t*, int32_t*, cudaStream_t);
-cudaError_t launch_indexer_topk_fused(const void*, const void*, const float*, const int32_t*,
-                                      const int32_t*, int64_t, float*, int64_t, int32_t*, int64_t,
-                                      int, int, int, uint32_t*, uint32_t*, int32_t*, cudaStream_t);
-cudaError_t launch_sparse_attn_simt(const void*, const void*, const void*, const void*,
-                                    const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
-                                    int, void*, int32_t*, cudaStream_t);
-cudaError_t launch_sparse_attn_tc(const void*, const void*, const void*, const void*,
-                                  const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
-                                  void*, int32_t*, cudaStream_t);
 size_t at_tc_workspace_bytes_auto(int tokens, int topk);
 cudaError_t launch_sparse_attn_mma(const void*, const void*, const void*, const void*,
                                    const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
                                    void*, int32_t*, cudaStream_t);
 int att_pick_splits(int tokens, int topk);
+
 cudaError_t launch_indexer_score_prefill(const void*, const void*, const float*, const int32_t*,
                                          const int32_t*, float*, int64_t, int, int, int, int,
                                          int32_t*, cudaStream_t);
@@ -69,12 +61,12 @@ const char* dsa_b200_error_string(int code) {
   return "dsa_b200: unknown error code";
 }
 
-// [ per request: max of the ordered score keys, max of their complements | control words and
-//   per-request histograms of the fused kernel | fp32 score rows ]
+// [ per request: max of the ordered score keys, max of their complements | per-request score
+//   histograms | fp32 score rows ]
 // The first two regions must be zero between calls (the kernels put back what they use), so each
 // has one fixed size for every shape: no call's score rows ever land on another call's words.
 constexpr size_t kMinmaxRegionBytes = 65536 * 2 * sizeof(uint32_t);   // batch <= 65535
-constexpr size_t kScoreRowsOffset = kMinmaxRegionBytes + dsa::kFusedRegionBytes;
+constexpr size_t kScoreRowsOffset = kMinmaxRegionBytes + dsa::kHistRegionBytes;
 size_t dsa_indexer_workspace_bytes(int batch, int max_pages) {
   if (batch <= 0 || max_pages <= 0) return 256;
   return kScoreRowsOffset + round256((size_t)batch * score_row_stride(max_pages) * sizeof(float));
@@ -83,18 +75,15 @@ size_t dsa_indexer_workspace_bytes(int batch, int max_pages) {
 // How dsa_indexer_topk scores and selects long rows (decode shapes, batch <= 1024):
 //   "hist"   (default) the scorer also builds every request's score histogram; the selection
 //            kernel starts from it (boundary bin, one counting and one writing sweep);
-//   "fused"  one kernel: requests are selected inside the scorer as their last chunk completes;
 //   "minmax" the scorer hands over each row's min / max, the selection builds its own histogram
-//            (also what larger batches and the shared-pages scorer use).
+//            over the linear map of that range (also what larger batches and the shared-pages
+//            scorer use).
 // DSA_INDEXER_PATH in the environment picks one; read on every call so that a test can compare
 // the paths in one process.
-enum IndexerPath { kPathHist, kPathFused, kPathMinmax };
+enum IndexerPath { kPathHist, kPathMinmax };
 static IndexerPath indexer_path() {
   const char* e = getenv("DSA_INDEXER_PATH");
-  if (e == nullptr) return kPathHist;
-  if (e[0] == 'f') return kPathFused;
-  if (e[0] == 'm') return kPathMinmax;
-  return kPathHist;
+  return (e != nullptr && e[0] == 'm') ? kPathMinmax : kPathHist;
 }
 
 static int scores_impl(const void* q_fp8, const void* k_cache, const float* weights,
@@ -174,21 +163,7 @@ int dsa_indexer_topk(const void* q_fp8, const void* k_cache, const float* weight
   uint32_t* minmax = shared_pages ? nullptr : static_cast<uint32_t*>(workspace);
   const bool long_rows = (int64_t)max_pages * dsa::kPage > dsa::kTopK;
   const IndexerPath path = indexer_path();
-  uint32_t* ghist = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + kMinmaxRegionBytes +
-                                                dsa::kFusedCtlBytes);
-  if (long_rows && !shared_pages && batch <= dsa::kFusedMaxBatch && path == kPathFused) {
-    // decode shapes: one kernel scores and selects (requests are selected as they complete,
-    // under the key stream of the later ones)
-    if (!q_fp8 || !k_cache || !weights || !seq_lens || !block_table || !topk_out)
-      return DSA_ERR_NULL_POINTER;
-    if (num_pages <= 0 || topk_stride < dsa::kTopK || block_table_stride < 0) return DSA_ERR_BAD_SHAPE;
-    if (!aligned16(q_fp8) || !aligned16(k_cache)) return DSA_ERR_MISALIGNED;
-    uint32_t* ctl = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + kMinmaxRegionBytes);
-    return static_cast<int>(dsa::launch_indexer_topk_fused(
-        q_fp8, k_cache, weights, seq_lens, block_table, block_table_stride, scores, stride, topk_out,
-        topk_stride, batch, num_pages, max_pages, ctl, ghist, status_dev,
-        static_cast<cudaStream_t>(stream)));
-  }
+  uint32_t* ghist = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + kMinmaxRegionBytes);
   // rows of at most 2048 tokens are emitted whole by the selection: their scores are skipped, and
   // when no row can be longer (max_pages <= 32) the scorer is not launched at all (the reference's
   // GPU dispatch takes the same shortcut from the shape alone, indexer_fused.py:358-380)

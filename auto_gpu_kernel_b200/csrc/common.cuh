@@ -53,16 +53,13 @@ __device__ __forceinline__ float ordered_to_float(uint32_t k) {
   return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
 }
 
-// Fused scorer + selection kernel: its region of the indexer workspace, in front of the score rows.
-// [ control words | per-request histograms ]; everything here is zero between calls (the kernel
-// puts back what it used), so the region has one fixed size whatever the batch.
-constexpr int kFusedMaxBatch = 1024;      // larger batches take the two-kernel path
-constexpr int kFusedBins = 4096;          // top 12 bits of the ordered score key
-constexpr int kFusedCtlNext = 0;          // next chunk to hand out
-constexpr int kFusedCtlExited = 1;        // CTAs that have left the kernel
-constexpr int kFusedCtlDone = 64;         // [kFusedMaxBatch] chunks completed per request
-constexpr size_t kFusedCtlBytes = 8192;
-constexpr size_t kFusedRegionBytes = kFusedCtlBytes + (size_t)kFusedMaxBatch * kFusedBins * sizeof(uint32_t);
+// Per-request score histograms (decode shapes): the scorer counts every score into 4096 bins over
+// the top 12 bits of its order-preserving key, the selection kernel starts from the finished
+// histogram and puts it back to zero.  The region sits in front of the score rows of the indexer
+// workspace and has one fixed size whatever the batch, so that it is zero between calls.
+constexpr int kHistMaxBatch = 1024;       // larger batches take the min/max path
+constexpr int kHistBins = 4096;
+constexpr size_t kHistRegionBytes = (size_t)kHistMaxBatch * kHistBins * sizeof(uint32_t);
 
 // -inf and NaN scores are ranked as this value by the selection (and by the scorer's min / max).
 constexpr float kScoreFloor = -3.0e38f;

@@ -42,7 +42,7 @@ constexpr uint32_t kIdescF8 = ptx::idesc(ptx::kFmtE4M3, ptx::kFmtE4M3, false, fa
 
 struct TcShared {
   // data[stage] and q[slot] sit in the 1024-byte aligned dynamic region before this struct
-  alignas(16) uint32_t hist[kFusedBins];   // kHist: counts of the current request's scores per key bin
+  alignas(16) uint32_t hist[kHistBins];   // kHist: counts of the current request's scores per key bin
   float scale[kTcStages][kTcTile];
   int prefix[kTcMaxBatch + 1];
   int partial[kTcThreads];
@@ -122,7 +122,7 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
     ptx::tmem_relinquish();
   }
   if (kHist) {
-    for (int i = tid; i < kFusedBins; i += kTcThreads) sh.hist[i] = 0;
+    for (int i = tid; i < kHistBins; i += kTcThreads) sh.hist[i] = 0;
   }
   ptx::grid_dependency_wait();  // q, weights, seq_lens, block_table and the cache may come from it
   // Only now may the selection kernel be scheduled (as SMs free up; it waits for our scores): it
@@ -304,10 +304,10 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
       auto flush_hist = [&](int req) -> bool {
         if (!group_sync()) return false;
         const int et = (warp - 2) * 32 + lane;
-        uint32_t* g = ghist + (size_t)req * kFusedBins;
+        uint32_t* g = ghist + (size_t)req * kHistBins;
         uint4* h4 = reinterpret_cast<uint4*>(sh.hist);
 #pragma unroll
-        for (int v = 0; v < kFusedBins / 4 / 128; ++v) {
+        for (int v = 0; v < kHistBins / 4 / 128; ++v) {
           const int q = v * 128 + et;
           const uint4 cnt = h4[q];
           if (cnt.x | cnt.y | cnt.z | cnt.w) {
@@ -413,7 +413,7 @@ cudaError_t launch_indexer_score_tc(const void* q_fp8, const void* k_cache, cons
                               kTcDynBytes, smem_opted_b);
     if (e != cudaSuccess) return e;
   }
-  if (ghist != nullptr && batch > kFusedMaxBatch) return cudaErrorInvalidValue;
+  if (ghist != nullptr && batch > kHistMaxBatch) return cudaErrorInvalidValue;
   CUtensorMap tmap_k;
   if (!make_rows128_map(&tmap_k, k_cache, (uint64_t)num_pages * 66)) return cudaErrorInvalidValue;
   for (int b0 = 0; b0 < batch; b0 += kTcMaxBatch) {

@@ -6,6 +6,8 @@
 // belongs to another runtime.  Such a caller cannot provide the score workspace that
 // dsa_indexer_topk asks for, so this entry point brings its own: a fixed array in the library's
 // device image.  The price is a size limit and a shared buffer (see below).
+#include <atomic>
+
 #include "common.cuh"
 
 namespace dsa {
@@ -24,7 +26,9 @@ constexpr size_t kNoAllocMaxScores = DSA_NOALLOC_MAX_SCORES;
 static __device__ __align__(256) float g_noalloc_scores[kNoAllocMaxScores];
 
 constexpr int kMaxDevices = 64;
-float* g_scores_addr[kMaxDevices];  // per device: device address of g_noalloc_scores (0 = not yet asked)
+// per device: device address of g_noalloc_scores (null = not yet asked); published atomically, so
+// host threads making their first call at once agree on it
+std::atomic<float*> g_scores_addr[kMaxDevices];
 
 // In host code `g_noalloc_scores` is only a handle for the runtime, not a device address: the
 // address a kernel can use comes from cudaGetSymbolAddress, asked once per device with that
@@ -34,13 +38,15 @@ int scores_address(float** out) {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (dev < 0 || dev >= kMaxDevices) return DSA_ERR_UNSUPPORTED;
-  if (g_scores_addr[dev] == nullptr) {
+  float* addr = g_scores_addr[dev].load(std::memory_order_acquire);
+  if (addr == nullptr) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_noalloc_scores);
     if (e != cudaSuccess) return static_cast<int>(e);
-    g_scores_addr[dev] = static_cast<float*>(p);
+    addr = static_cast<float*>(p);
+    g_scores_addr[dev].store(addr, std::memory_order_release);
   }
-  *out = g_scores_addr[dev];
+  *out = addr;
   return DSA_OK;
 }
 

@@ -51,6 +51,41 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
   }
 }
 
+// ---- across the CTAs of a cluster: the barrier lives in the PEER's shared memory --------------
+// Shared-memory address of the same variable in CTA `rank` of the cluster (shared::cluster window).
+__device__ __forceinline__ uint32_t map_to_peer(uint32_t local_addr, int rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  return remote;
+}
+// One arrival on a barrier of another CTA of the cluster; release at cluster scope, so stores made
+// before it (to that CTA's shared memory too) are visible to whoever acquires the barrier there.
+__device__ __forceinline__ void mbar_arrive_peer(uint32_t remote_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// mbar_wait for a barrier that a peer CTA arrives on (acquire at cluster scope); same time limit.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
+                                                  uint64_t limit_ns = 250000000ull) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t spins = 0;; ++spins) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if ((spins & 63u) == 63u && global_timer_ns() - t0 > limit_ns) return false;
+  }
+}
+__device__ __forceinline__ void fence_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

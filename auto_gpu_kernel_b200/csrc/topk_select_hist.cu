@@ -149,8 +149,8 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
 
   // ---- (1) histogram -> boundary bin, while the slice travels into shared memory ----------------
   // thread t owns bins 4095-4t .. 4092-4t (one 16-byte load), so thread order is rank order
-  uint4* g4 = reinterpret_cast<uint4*>(ghist + (size_t)b * kFusedBins);
-  const uint4 h = __ldcg(g4 + (kFusedBins / 4 - 1 - tid));
+  uint4* g4 = reinterpret_cast<uint4*>(ghist + (size_t)b * kHistBins);
+  const uint4 h = __ldcg(g4 + (kHistBins / 4 - 1 - tid));
   if (staged) {
     const int n4 = vec ? (seg_len & ~3) : 0;
     for (int i = tid * 4; i < n4; i += kShThreads * 4)
@@ -167,7 +167,7 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         if (!found && run + c[k] >= (uint32_t)kTopK) {
-          sh.edge = (uint32_t)(kFusedBins - 1 - 4 * tid - k); sh.above = run; sh.in_edge = c[k];
+          sh.edge = (uint32_t)(kHistBins - 1 - 4 * tid - k); sh.above = run; sh.in_edge = c[k];
           found = true;
         }
         run += c[k];
@@ -210,7 +210,7 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
     peer->peer_cnd[crank] = totals >> 16;
   }
   cluster.sync();
-  if (crank == 0 && tid < kFusedBins / 4) g4[tid] = make_uint4(0u, 0u, 0u, 0u);   // every CTA has read it
+  if (crank == 0 && tid < kHistBins / 4) g4[tid] = make_uint4(0u, 0u, 0u, 0u);   // every CTA has read it
   uint32_t sel_at = excl & 0xFFFFu, cnd_at = excl >> 16, nc = 0, sel_all = 0;
   for (int r = 0; r < csize; ++r) {
     if (r < crank) { sel_at += sh.peer_sel[r]; cnd_at += sh.peer_cnd[r]; }
@@ -357,7 +357,7 @@ static int sh_cluster_size(int batch, int max_len) {
 bool topk_select_hist_supports(int batch, int max_pages) {
   const int c = sh_cluster_size(batch, max_pages * kPage);
   const int64_t seg = ((int64_t)max_pages * kPage + c - 1) / c;
-  return batch <= kFusedMaxBatch && (seg <= kShRowCap || seg < 65536);
+  return batch <= kHistMaxBatch && (seg <= kShRowCap || seg < 65536);
 }
 
 cudaError_t launch_topk_select_hist(const float* scores, int64_t score_stride, const int32_t* seq_lens,

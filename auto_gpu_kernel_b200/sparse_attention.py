@@ -21,8 +21,7 @@ KPE = 64
 def kernel(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale, output, lse, variant=0):
     """Write attention output and base-2 LSE in place; enqueued on the current stream, returns None.
     `variant` 0 = default (warp-level mma.sync) kernel, 1 = CUDA-core cross-check kernel, 2 =
-    tcgen05/TMEM kernel (not part of the reference
-    signature; positional callers never pass it)."""
+    tcgen05/TMEM kernel (not part of the reference signature; positional callers never pass it)."""
     if not q_nope.is_cuda:
         raise RuntimeError("dsa sparse attention: CUDA tensors required (this operator has no CPU path)")
     dev = q_nope.device

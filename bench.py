@@ -471,9 +471,12 @@ def fp8_peak_tflops(dev):
 def run_comparators(args, ranks):
     """The reference's GPU kernels (baseline/_ref) beside this library's, same inputs, same events.
     Only dispatches that take no in-kernel spin barrier: the second-generation attention at
-    T = 64 (4 splits x 64 tokens = 256 CTAs > 144: true-last-CTA merge) and the second-generation
-    indexer at B = 64 x 8191 tokens (its 13-bit position field ends there; 64 x 4 chunks > 128:
-    the unfused sort + merge pair, not the flag-synchronised kernel)."""
+    T = 64 (4 splits x 64 tokens = 256 CTAs > 144: true-last-CTA merge) and at T = 256 (no split),
+    the second-generation indexer at B = 64 x 8191 tokens (its 13-bit position field ends there;
+    64 x 4 chunks > 128: the unfused sort + merge pair, not the flag-synchronised kernel) and on
+    short rows (one fill kernel), the contest submissions' indexer (no barrier in the file) and
+    their attention at T <= 2.  A kernel that fails to build or launch on this box is recorded with
+    the error text."""
     from auto_gpu_kernel_b200 import indexer, inputs as wl, sparse_attention
     dev = ranks.dev
     result = {}
@@ -501,34 +504,50 @@ def run_comparators(args, ranks):
     if not (REF_DIR / "fable_attention.py").exists():
         return {"unavailable": "baseline/_ref is empty: run baseline/fetch_reference.py on a checkout of the reference"}
 
-    # attention, cfg1
-    lens = wl.uniform_lengths(64, 8192, 32768, seed=1)
-    att = wl.make_attention_inputs(lens, seed=1, device=dev)
-    out_a, lse_a = torch.empty_like(att.q_nope), torch.empty(64, 16, dtype=torch.float32, device=dev)
-    out_b, lse_b = torch.empty_like(att.q_nope), torch.empty(64, 16, dtype=torch.float32, device=dev)
-    time_pair("attention_cfg1_T64",
-              lambda: sparse_attention.kernel(*att.args(), out_a, lse_a),
-              "fable_attention",
-              lambda mod: mod.kernel(*att.args(), out_b, lse_b),
-              lambda: {"max_abs_out": float((out_a.float() - out_b.float()).abs().max()),
-                       "max_abs_lse": float((lse_a - lse_b).abs().max())})
-    del att
-    # indexer, B = 64 x 8191
-    inp = wl.make_indexer_inputs([8191] * 64, seed=7, device=dev)
-    top_a = torch.empty(64, TOPK, dtype=torch.int32, device=dev)
-    top_b = torch.empty(64, TOPK, dtype=torch.int32, device=dev)
+    def attention_pair(label, theirs, lens, seed, pad_tail=0):
+        att = wl.make_attention_inputs(lens, seed=seed, device=dev, pad_tail=pad_tail)
+        n = len(lens)
+        out_a, lse_a = torch.empty_like(att.q_nope), torch.empty(n, 16, dtype=torch.float32, device=dev)
+        out_b, lse_b = torch.empty_like(att.q_nope), torch.empty(n, 16, dtype=torch.float32, device=dev)
+        time_pair(label, lambda: sparse_attention.kernel(*att.args(), out_a, lse_a), theirs,
+                  lambda mod: mod.kernel(*att.args(), out_b, lse_b),
+                  lambda: {"max_abs_out": float((out_a.float() - out_b.float()).abs().max()),
+                           "max_abs_lse": float((lse_a - lse_b).nan_to_num(neginf=0.0).abs().max())})
 
-    def overlap():
-        a, b = torch.sort(top_a, dim=1).values, torch.sort(top_b, dim=1).values
-        same = sum(len(set(x.tolist()) & set(y.tolist())) for x, y in zip(a.cpu(), b.cpu()))
-        return {"mean_set_overlap": same / (64 * TOPK),
-                "note": "the reference ranks by the top 19 key bits, this library exactly"}
+    def indexer_pair(label, theirs, lens, seed, note):
+        inp = wl.make_indexer_inputs(lens, seed=seed, device=dev)
+        top_a = torch.empty(len(lens), TOPK, dtype=torch.int32, device=dev)
+        top_b = torch.empty(len(lens), TOPK, dtype=torch.int32, device=dev)
 
-    time_pair("indexer_B64_ctx8191",
-              lambda: indexer.kernel(*inp.args(), top_a),
-              "fable_indexer",
-              lambda mod: mod.kernel(*inp.args(), top_b),
-              overlap)
+        def overlap():
+            a, b = top_a.cpu(), top_b.cpu()
+            same = sum(len(set(x.tolist()) & set(y.tolist())) for x, y in zip(a, b))
+            want = sum(min(n, TOPK) + (1 if n < TOPK else 0) for n in lens)   # the -1 pad counts once
+            return {"mean_set_overlap": same / max(want, 1), "note": note}
+
+        time_pair(label, lambda: indexer.kernel(*inp.args(), top_a), theirs,
+                  lambda mod: mod.kernel(*inp.args(), top_b), overlap)
+
+    # ---- the configurations of this benchmark ------------------------------------------------------
+    # second-generation attention at cfg1: 64 tokens x 4 splits = 256 CTAs > 144 -> true-last-CTA merge
+    attention_pair("attention_cfg1_T64", "fable_attention", wl.uniform_lengths(64, 8192, 32768, seed=1), 1)
+    # ... and at 256 tokens, where it does not split at all (one CTA per token, no merge)
+    attention_pair("attention_T256_ctx8K", "fable_attention", [8192] * 256, 2)
+    # second-generation indexer at the longest context its 13-bit position field allows
+    indexer_pair("indexer_B64_ctx8191", "fable_indexer", [8191] * 64, 7,
+                 "the reference ranks by the top 19 key bits, this library exactly")
+    # ---- contest-like shapes (B <= 31, contexts up to 5806, tail-padded index rows) ---------------
+    # the contest submissions; only their dispatches without a spin barrier: the indexer (none in
+    # the file), the attention at T <= 2 (every CTA recomputes the logits, no exchange)
+    gen = torch.Generator().manual_seed(11)
+    ragged = [int(x) for x in torch.randint(2049, 5807, (31,), generator=gen)]
+    ragged[0], ragged[7], ragged[19] = 5806, 94, 1500
+    indexer_pair("indexer_contest_B31_ctx5806", "indexer_fused", ragged, 11,
+                 "both exact; rows of at most 2048 tokens are emitted whole by both")
+    short = [int(x) for x in torch.randint(1, 2049, (16,), generator=gen)]
+    indexer_pair("indexer_contest_B16_short", "indexer_fused", short, 12, "no scoring: every token is selected")
+    indexer_pair("indexer_contest_B16_short_gen2", "fable_indexer", short, 12, "no scoring: every token is selected")
+    attention_pair("attention_contest_T2_padded", "sparse_fused", [33, 1200], 13)
     return result
 
 

@@ -242,6 +242,15 @@ typedef struct dsa_host_step_args {
 
 int dsa_decode_step_host(const dsa_host_step_args* args);
 
+/* Self-test of the bounded device-side waits (no counterpart in the reference, whose kernels spin
+ * without a limit: sparse_fused.py:135-137).  One thread waits for at most `limit_ns` nanoseconds
+ * (1 .. 1e9) on a barrier that receives no arrival, then sets DSA_STATUS_WAIT_TIMEOUT in
+ * *status_dev and stores the time it waited in *waited_ns_dev (may be NULL).  Nothing faults or
+ * hangs; the context stays usable.  This is the path every pipeline of the library takes when an
+ * arrival is lost. */
+int dsa_selftest_wait_expiry(uint64_t limit_ns, int32_t* status_dev, uint64_t* waited_ns_dev,
+                             void* stream);
+
 #ifdef __cplusplus
 }
 #endif

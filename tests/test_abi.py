@@ -34,8 +34,8 @@ def test_library_builds_and_exports_every_declared_symbol():
 
 def test_host_side_argument_errors():
     lib = _lib.load()
-    # min/max words (512 KB) + fused kernel's control words (8 KB) and 1024 histograms of 4096 bins + score rows
-    assert lib.dsa_indexer_workspace_bytes(64, 512) == 512 * 1024 + 8192 + 1024 * 4096 * 4 + 64 * 512 * 64 * 4
+    # min/max words (512 KB) + 1024 score histograms of 4096 bins + score rows
+    assert lib.dsa_indexer_workspace_bytes(64, 512) == 512 * 1024 + 1024 * 4096 * 4 + 64 * 512 * 64 * 4
     assert lib.dsa_indexer_workspace_bytes(1, 1) % 256 == 0
     assert lib.dsa_sparse_attn_workspace_bytes(64, 16, 2048) > 64 * 16 * 512 * 4
     # batch 0 is a no-op; null pointers and bad shapes are reported without touching the device

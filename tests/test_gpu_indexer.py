@@ -234,3 +234,39 @@ def test_cpu_tensors_are_rejected():
     inp = wl.make_indexer_inputs([100], seed=0)
     with pytest.raises(RuntimeError, match="no CPU path"):
         indexer.run(*inp.args())
+
+
+def test_short_rows_chained_with_attention_on_one_index_buffer(cuda):
+    """Contexts within top-k: no scorer is launched, so the selection is the programmatic dependent
+    of whatever ran before it -- here the previous step's attention, which reads the very index
+    buffer the selection rewrites.  Many steps back to back on one stream with changing lengths:
+    every step's attention must have seen that step's indices, none of the next step's."""
+    from auto_gpu_kernel_b200 import sparse_attention
+    batch, steps = 8, 24
+    block = wl.make_decode_block_inputs([2048] * batch, seed=19, device=cuda)
+    idx = block.indexer
+    assert idx.block_table.shape[1] == 32
+    gen = torch.Generator().manual_seed(20)
+    lens = [torch.randint(1, 2049, (batch,), generator=gen).to(torch.int32) for _ in range(steps)]
+    lens_dev = [x.to(cuda) for x in lens]
+    topk = torch.empty(batch, 2048, dtype=torch.int32, device=cuda)
+    outs = [torch.empty_like(block.q_nope) for _ in range(steps)]
+    lses = [torch.empty(batch, 16, dtype=torch.float32, device=cuda) for _ in range(steps)]
+    torch.cuda.synchronize()
+    for s in range(steps):
+        indexer.kernel(idx.q_index_fp8, idx.k_index_cache_fp8, idx.weights, lens_dev[s], idx.block_table, topk)
+        sparse_attention.kernel(block.q_nope, block.q_pe, block.ckv_cache, block.kpe_cache, topk,
+                                block.sm_scale, outs[s], lses[s])
+    workspace.check_status(cuda)
+    table = idx.block_table.cpu().long()
+    pos = torch.arange(2048)
+    for s in range(steps):
+        want = torch.full((batch, 2048), -1, dtype=torch.int32)
+        for b in range(batch):
+            n = int(lens[s][b])
+            want[b, :n] = (table[b, pos[:n] // 64] * 64 + pos[:n] % 64).to(torch.int32)
+        ref_out, ref_lse = oracle.sparse_attention(block.q_nope, block.q_pe, block.ckv_cache, block.kpe_cache,
+                                                   want.to(cuda), block.sm_scale,
+                                                   output=torch.empty_like(outs[s]), lse=torch.empty_like(lses[s]))
+        assert torch.allclose(lses[s], ref_lse, atol=1e-3, rtol=1e-3), f"step {s}"
+        assert torch.allclose(outs[s].float(), ref_out.float(), atol=1e-2, rtol=1e-2), f"step {s}"

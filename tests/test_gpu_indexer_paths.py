@@ -1,7 +1,7 @@
-"""The histogram-based selection paths of dsa_indexer_topk -- "hist" (default: the scorer builds
-each request's histogram, a lean selection kernel follows) and "fused" (one kernel, requests are
-selected inside the scorer as they complete) -- driven through the C ABI with score rows chosen
-by the test: `indexer_inputs_from_scores` builds a key cache whose scores are exactly a given fp32
+"""The two selection paths of dsa_indexer_topk -- "hist" (default: the scorer builds each request's
+score histogram, the selection kernel starts from it) and "minmax" (the scorer hands over the
+row's min / max, the selection builds a histogram of its own) -- driven through the C ABI with
+score rows chosen by the test: `indexer_inputs_from_scores` builds a key cache whose scores are exactly a given fp32
 row, so the selection logic (boundary bin, candidate ranking, the radix descent for over-full
 bins, tie order, short rows, many requests) is checked against torch.topk on known rows."""
 import pytest
@@ -14,7 +14,7 @@ from helpers import assert_topk_matches, indexer_inputs_from_scores
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=["hist", "fused"], autouse=True)
+@pytest.fixture(params=["hist", "minmax"], autouse=True)
 def indexer_path(request, monkeypatch):
     """Every test of this file runs once per path (DSA_INDEXER_PATH is read on every call)."""
     monkeypatch.setenv("DSA_INDEXER_PATH", request.param)
@@ -103,8 +103,8 @@ def test_nan_and_inf_rank_lowest(cuda):
 
 
 def test_many_requests_complete_in_any_order(cuda):
-    """More requests than the kernel has CTAs per SM pair, ragged lengths with short and empty
-    rows in between: requests are selected as their last chunk completes, by whichever CTA that is."""
+    """More requests than SMs, ragged lengths with short and empty rows in between; and a second
+    call over the same workspace: whatever a call leaves behind must not disturb the next."""
     gen = torch.Generator().manual_seed(77)
     lens = [int(x) for x in torch.randint(2049, 9000, (150,), generator=gen)]
     for i in range(0, 150, 11):
@@ -121,12 +121,14 @@ def test_many_requests_complete_in_any_order(cuda):
     for b, n in enumerate(lens):
         _check_row(rows[b], n, table[b], got2[b], label=f"second call, request {b}")
     ws = workspace.get(cuda, "indexer", 1)
-    fused = ws[512 * 1024: 512 * 1024 + 8192 + 1024 * 4096 * 4].view(torch.int32)
+    zero_between_calls = ws[: 512 * 1024 + 1024 * 4096 * 4].view(torch.int32)   # min/max words, histograms
     torch.cuda.synchronize()
-    assert int(fused.abs().max()) == 0
+    assert int(zero_between_calls.abs().max()) == 0
 
 
 def test_paths_select_the_same_set(cuda, monkeypatch, indexer_path):
+    if indexer_path == "minmax":
+        pytest.skip("compared from the other side")
     lens = [3000, 2049, 40000, 9000, 100, 0, 33000]
     inp = wl.make_indexer_inputs(lens, seed=31, device=cuda)
     rows = [r.cpu() for r in oracle.indexer_scores(*inp.args())]

@@ -8,7 +8,9 @@ already run every other test."""
 import pytest
 import torch
 
+import dsa_oracle as oracle
 from auto_gpu_kernel_b200 import _lib, indexer, inputs as wl, workspace
+from helpers import assert_topk_matches
 
 pytestmark = pytest.mark.gpu
 
@@ -38,6 +40,9 @@ def test_noalloc_matches_workspace_entry_point_twice(cuda):
         workspace.check_status(cuda)
         # the selected SET is deterministic (bit-exact integer output up to order within a row)
         assert torch.equal(torch.sort(got, dim=1).values, torch.sort(want, dim=1).values)
+        # and it stands on its own against the oracle (acceptance rule of the definition)
+        rows = [r.cpu() for r in oracle.indexer_scores(*inp.args())]
+        assert_topk_matches(inp, got, rows, label=f"noalloc seed {seed}")
 
 
 def test_noalloc_rejects_sizes_beyond_its_scratch(cuda):
