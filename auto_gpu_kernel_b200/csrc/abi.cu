@@ -17,12 +17,17 @@ cudaError_t launch_topk_select_hist(const float*, int64_t, const int32_t*, const
 bool topk_select_hist_supports(int batch, int max_pages);
 cudaError_t launch_topk_select(const float*, int64_t, const int32_t*, const int32_t*, int64_t,
                                int32_t*, int64_t, int, int, uint32_t*, int32_t*, cudaStream_t);
+cudaError_t launch_sparse_attn_simt(const void*, const void*, const void*, const void*,
+                                    const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
+                                    int, void*, int32_t*, cudaStream_t);
+cudaError_t launch_sparse_attn_tc(const void*, const void*, const void*, const void*,
+                                  const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
+                                  void*, int32_t*, cudaStream_t);
 size_t at_tc_workspace_bytes_auto(int tokens, int topk);
 cudaError_t launch_sparse_attn_mma(const void*, const void*, const void*, const void*,
                                    const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
                                    void*, int32_t*, cudaStream_t);
 int att_pick_splits(int tokens, int topk);
-
 cudaError_t launch_indexer_score_prefill(const void*, const void*, const float*, const int32_t*,
                                          const int32_t*, float*, int64_t, int, int, int, int,
                                          int32_t*, cudaStream_t);
