@@ -112,7 +112,7 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
   const int crank = (int)cluster.block_rank();
 
   const int b = blockIdx.x / csize;
-  const int tid = threadIdx.x, lane = tid & 31;
+  const int tid = threadIdx.x;
   int len = seq_lens[b];
   len = max(0, min(len, max_pages * kPage));
   int32_t* out_row = out + (size_t)b * out_stride;
@@ -151,11 +151,15 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
   // thread t owns bins 4095-4t .. 4092-4t (one 16-byte load), so thread order is rank order
   uint4* g4 = reinterpret_cast<uint4*>(ghist + (size_t)b * kHistBins);
   const uint4 h = __ldcg(g4 + (kHistBins / 4 - 1 - tid));
+  // a staged slice is kept as order-preserving KEYS: the sweeps below then only compare integers
+  uint32_t* key_s = reinterpret_cast<uint32_t*>(row_s);
+  const int n4s = staged && vec ? (seg_len & ~3) : 0;   // elements handled four at a time
   if (staged) {
-    const int n4 = vec ? (seg_len & ~3) : 0;
-    for (int i = tid * 4; i < n4; i += kShThreads * 4)
-      *reinterpret_cast<float4*>(row_s + i) = __ldcg(reinterpret_cast<const float4*>(row + seg_lo + i));
-    for (int i = n4 + tid; i < seg_len; i += kShThreads) row_s[i] = __ldcg(row + seg_lo + i);
+    for (int i = tid * 4; i < n4s; i += kShThreads * 4) {
+      const float4 q = __ldcg(reinterpret_cast<const float4*>(row + seg_lo + i));
+      *reinterpret_cast<uint4*>(key_s + i) = make_uint4(sh_key(q.x), sh_key(q.y), sh_key(q.z), sh_key(q.w));
+    }
+    for (int i = n4s + tid; i < seg_len; i += kShThreads) key_s[i] = sh_key(__ldcg(row + seg_lo + i));
   }
   {
     const uint32_t mine = h.x + h.y + h.z + h.w;
@@ -182,23 +186,42 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
   }
   const uint32_t need = (uint32_t)kTopK - above;   // elements wanted from the boundary bin (>= 1)
   const bool few = in_edge <= (uint32_t)kShCandCap;
-  auto key_at = [&](int i) -> uint32_t { return sh_key(staged ? row_s[i - seg_lo] : __ldcg(row + i)); };
+  auto key_at = [&](int i) -> uint32_t { return staged ? key_s[i - seg_lo] : sh_key(__ldcg(row + i)); };
+  // key > hi_edge: above the boundary bin; key - lo_edge < 2^20 (unsigned): inside it
+  const uint32_t lo_edge = edge << kShBinShift, hi_edge = lo_edge | 0xFFFFFu;
 
-  // ---- (2) counting sweep --------------------------------------------------------------------------
-  // A thread owns four consecutive elements per step; both sweeps walk them in the same order.
+  // ---- (2) classification ---------------------------------------------------------------------------
+  // A thread owns four consecutive elements per step of 4096 (at most 11 steps of a staged slice)
+  // plus at most one element of the ragged end: one pass turns them into two bit masks (bit 4 s + e
+  // for element e of step s, bit 63 for the ragged one), kept in registers for the writing pass.
+  // A streamed slice (too long to stage) is swept from L2 twice instead.
+  const bool fast = staged && seg_len <= 44 * kShThreads + 3 * kShThreads && (seg_len - n4s) <= kShThreads;
+  uint64_t sel_mask = 0, cnd_mask = 0;
   uint32_t n_sel = 0, n_cnd = 0;
-  const int n4s = staged ? (seg_len & ~3) : 0;
-  for (int i = tid * 4; i < n4s; i += kShThreads * 4) {
-    const float4 q = *reinterpret_cast<const float4*>(row_s + i);
-    const uint32_t b0 = sh_key(q.x) >> kShBinShift, b1 = sh_key(q.y) >> kShBinShift;
-    const uint32_t b2 = sh_key(q.z) >> kShBinShift, b3 = sh_key(q.w) >> kShBinShift;
-    n_sel += (b0 > edge) + (b1 > edge) + (b2 > edge) + (b3 > edge);
-    n_cnd += (b0 == edge) + (b1 == edge) + (b2 == edge) + (b3 == edge);
-  }
-  for (int i = seg_lo + n4s + tid; i < seg_hi; i += kShThreads) {
-    const uint32_t bin = key_at(i) >> kShBinShift;
-    n_sel += bin > edge;
-    n_cnd += bin == edge;
+  if (fast) {
+    int step = 0;
+    for (int i = tid * 4; i < n4s; i += kShThreads * 4, ++step) {
+      const uint4 k = *reinterpret_cast<const uint4*>(key_s + i);
+      const uint32_t ks[4] = {k.x, k.y, k.z, k.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        sel_mask |= (uint64_t)(ks[e] > hi_edge) << (4 * step + e);
+        cnd_mask |= (uint64_t)(ks[e] - lo_edge < 0x100000u) << (4 * step + e);
+      }
+    }
+    if (n4s + tid < seg_len) {
+      const uint32_t k = key_s[n4s + tid];
+      sel_mask |= (uint64_t)(k > hi_edge) << 63;
+      cnd_mask |= (uint64_t)(k - lo_edge < 0x100000u) << 63;
+    }
+    n_sel = (uint32_t)__popcll(sel_mask);
+    n_cnd = (uint32_t)__popcll(cnd_mask);
+  } else {
+    for (int i = seg_lo + tid; i < seg_hi; i += kShThreads) {
+      const uint32_t k = key_at(i);
+      n_sel += k > hi_edge;
+      n_cnd += k - lo_edge < 0x100000u;
+    }
   }
   uint32_t totals = 0;
   const uint32_t excl = sh_block_excl_scan(n_sel | (n_cnd << 16), sh.warp_sums, &totals);
@@ -219,26 +242,38 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
   }
   if (crank == 0 && tid == 0 && (sel_all != above || nc != in_edge)) raise_status(status, DSA_STATUS_TOPK_COUNT);
 
-  // ---- (3) writing sweep: selected elements to their places, boundary bin to the candidate list --
+  // ---- (3) writing pass: selected elements to their places, boundary bin to the candidate list ---
   ShShared* first = cluster.map_shared_rank(&sh, 0);
-  auto place = [&](int i, uint32_t key) {
-    const uint32_t bin = key >> kShBinShift;
-    if (bin > edge) {
-      if (sel_at < (uint32_t)kTopK) out_row[sel_at] = slot_of(i);
+  if (fast) {
+    // element of mask bit `bit`, as a position in the row
+    auto position = [&](int bit) -> int {
+      return bit == 63 ? seg_lo + n4s + tid : seg_lo + tid * 4 + (bit >> 2) * (kShThreads * 4) + (bit & 3);
+    };
+    while (sel_mask) {
+      const int bit = __ffsll((long long)sel_mask) - 1;
+      sel_mask &= sel_mask - 1;
+      if (sel_at < (uint32_t)kTopK) out_row[sel_at] = slot_of(position(bit));
       ++sel_at;
-    } else if (bin == edge) {
-      if (few && cnd_at < (uint32_t)kShCandCap) { first->cand_key[cnd_at] = key; first->cand_idx[cnd_at] = (uint32_t)i; }
+    }
+    while (few && cnd_mask) {
+      const int bit = __ffsll((long long)cnd_mask) - 1;
+      cnd_mask &= cnd_mask - 1;
+      const int i = position(bit);
+      if (cnd_at < (uint32_t)kShCandCap) { first->cand_key[cnd_at] = key_s[i - seg_lo]; first->cand_idx[cnd_at] = (uint32_t)i; }
       ++cnd_at;
     }
-  };
-  for (int i = tid * 4; i < n4s; i += kShThreads * 4) {
-    const float4 q = *reinterpret_cast<const float4*>(row_s + i);
-    place(seg_lo + i, sh_key(q.x));
-    place(seg_lo + i + 1, sh_key(q.y));
-    place(seg_lo + i + 2, sh_key(q.z));
-    place(seg_lo + i + 3, sh_key(q.w));
+  } else {
+    for (int i = seg_lo + tid; i < seg_hi; i += kShThreads) {
+      const uint32_t k = key_at(i);
+      if (k > hi_edge) {
+        if (sel_at < (uint32_t)kTopK) out_row[sel_at] = slot_of(i);
+        ++sel_at;
+      } else if (k - lo_edge < 0x100000u) {
+        if (few && cnd_at < (uint32_t)kShCandCap) { first->cand_key[cnd_at] = k; first->cand_idx[cnd_at] = (uint32_t)i; }
+        ++cnd_at;
+      }
+    }
   }
-  for (int i = seg_lo + n4s + tid; i < seg_hi; i += kShThreads) place(i, key_at(i));
   cluster.sync();   // candidates are in the first CTA's shared memory; the peers are done
   if (crank != 0) return;
 

@@ -121,9 +121,10 @@ def test_many_requests_complete_in_any_order(cuda):
     for b, n in enumerate(lens):
         _check_row(rows[b], n, table[b], got2[b], label=f"second call, request {b}")
     ws = workspace.get(cuda, "indexer", 1)
-    zero_between_calls = ws[: 512 * 1024 + 1024 * 4096 * 4].view(torch.int32)   # min/max words, histograms
     torch.cuda.synchronize()
-    assert int(zero_between_calls.abs().max()) == 0
+    minmax_words = ws[: 2 * 4 * len(lens)].view(torch.int32)                        # this batch's min/max words
+    histograms = ws[512 * 1024: 512 * 1024 + 1024 * 4096 * 4].view(torch.int32)    # all 1024 histograms
+    assert int(minmax_words.abs().max()) == 0 and int(histograms.abs().max()) == 0
 
 
 def test_paths_select_the_same_set(cuda, monkeypatch, indexer_path):
