@@ -52,10 +52,11 @@ def _run(rows, lens, cuda, seed=0):
     return inp, out.cpu()
 
 
-@pytest.mark.parametrize("length", [2049, 5000, 5003, 45057, 131072])
+@pytest.mark.parametrize("length", [2049, 5000, 5003, 45057, 131072, 200001])
 def test_selection_against_torch_topk(cuda, length):
     """Positive, negative, mixed and one-binade rows (the last puts the whole row into one bin of
-    the first histogram, so it takes the radix descent), lengths that are not multiples of 4 or 128."""
+    the first histogram, so it takes the radix descent), lengths that are not multiples of 4 or 128,
+    and one beyond what four CTAs can stage in shared memory (the slices are then swept from L2)."""
     gen = torch.Generator().manual_seed(length)
     width = (length + 63) // 64 * 64
     rows = torch.randn(4, width, generator=gen)
