@@ -103,7 +103,7 @@ def test_nan_and_inf_rank_lowest(cuda):
     assert sorted(i for i in taken.tolist() if i < 4000) == list(range(1048))   # lowest positions first
 
 
-def test_many_requests_complete_in_any_order(cuda):
+def test_many_requests_complete_in_any_order(cuda, indexer_path):
     """More requests than SMs, ragged lengths with short and empty rows in between; and a second
     call over the same workspace: whatever a call leaves behind must not disturb the next."""
     gen = torch.Generator().manual_seed(77)
@@ -123,9 +123,10 @@ def test_many_requests_complete_in_any_order(cuda):
         _check_row(rows[b], n, table[b], got2[b], label=f"second call, request {b}")
     ws = workspace.get(cuda, "indexer", 1)
     torch.cuda.synchronize()
-    minmax_words = ws[: 2 * 4 * len(lens)].view(torch.int32)                        # this batch's min/max words
     histograms = ws[512 * 1024: 512 * 1024 + 1024 * 4096 * 4].view(torch.int32)    # all 1024 histograms
-    assert int(minmax_words.abs().max()) == 0 and int(histograms.abs().max()) == 0
+    assert int(histograms.abs().max()) == 0
+    if indexer_path == "minmax":     # the words of this batch's requests (the other path never touches them)
+        assert int(ws[: 2 * 4 * len(lens)].view(torch.int32).abs().max()) == 0
 
 
 def test_paths_select_the_same_set(cuda, monkeypatch, indexer_path):
