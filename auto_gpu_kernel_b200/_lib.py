@@ -45,6 +45,7 @@ SIGNATURES = {
                                      _ptr, _ptr]),
     "dsa_decode_step_host": (_c_int, [_ptr]),
     "dsa_selftest_wait_expiry": (_c_int, [ctypes.c_uint64, _ptr, _ptr, _ptr]),
+    "dsa_selftest_mma_rate": (_c_int, [_c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr]),
 }
 
 

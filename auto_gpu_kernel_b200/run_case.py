@@ -6,6 +6,7 @@
     python -m auto_gpu_kernel_b200.run_case attention --batch 64 --context 8192 --variant 0
     python -m auto_gpu_kernel_b200.run_case block     --batch 64 --context 32768
     python -m auto_gpu_kernel_b200.run_case prefill   --batch 4096 --context 16384
+    python -m auto_gpu_kernel_b200.run_case mma-rate         (issue cost of tcgen05.mma / mma.sync shapes)
 
 Meant for profilers (the launches of one kernel in a small process) and for quick A/B timing.
 The time printed is CUDA-event time over `--iters` back-to-back launches after `--warmup` ones.
@@ -20,9 +21,46 @@ import os
 import sys
 
 
+def measure_mma_rate(dev, kind, m, n, iters=2880):
+    """(issue cycles, completion cycles) per instruction of `dsa_selftest_mma_rate` (see the header)."""
+    import torch
+    from . import _lib, workspace
+    lib = _lib.load()
+    cycles = torch.zeros(2, dtype=torch.int64, device=dev)
+    sink = torch.zeros(1, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.dsa_selftest_mma_rate(kind, m, n, iters, cycles.data_ptr(), sink.data_ptr(),
+                                       workspace.status_word(dev).data_ptr(),
+                                       torch.cuda.current_stream(dev).cuda_stream)
+    _lib.check(rc, "dsa_selftest_mma_rate")
+    torch.cuda.synchronize(dev)
+    workspace.check_status(dev)
+    per = iters * (8 * m if kind == 2 else 1)      # mma.sync: 8 per warp and iteration, m warps
+    return cycles[0].item() / per, cycles[1].item() / per
+
+
+def mma_rate(dev) -> int:
+    """Cost of one tensor-core instruction, per SM: tcgen05.mma (one issuing thread) for the shapes
+    the kernels use or could use, and mma.sync m16n8k16 issued from 4 / 8 / 16 warps."""
+    rows = []
+    for kind, name in ((0, "tcgen05 bf16"), (1, "tcgen05 e4m3")):
+        for m in (64, 128):
+            for n in (16, 64, 128, 256):
+                issue, done = measure_mma_rate(dev, kind, m, n)
+                rows.append({"instr": name, "m": m, "n": n, "issue_cycles": round(issue, 1),
+                             "complete_cycles": round(done, 1)})
+    for warps in (4, 8, 16):
+        _, done = measure_mma_rate(dev, 2, warps, 0, iters=2000)
+        rows.append({"instr": "mma.sync m16n8k16 bf16", "warps": warps, "cycles_per_instr_per_sm": round(done, 2),
+                     "mac_per_clk_per_sm": round(2048 / done)})
+    for r in rows:
+        print(json.dumps(r))
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("case", choices=["scorer", "select", "indexer", "attention", "block", "prefill"])
+    ap.add_argument("case", choices=["scorer", "select", "indexer", "attention", "block", "prefill", "mma-rate"])
     ap.add_argument("--batch", type=int, default=64, help="requests (= query tokens)")
     ap.add_argument("--context", type=int, default=32768, help="tokens per request")
     ap.add_argument("--iters", type=int, default=20)
@@ -43,6 +81,8 @@ def main(argv=None) -> int:
         print("run_case: no CUDA device", file=sys.stderr)
         return 2
     dev = torch.device("cuda", 0)
+    if args.case == "mma-rate":
+        return mma_rate(dev)
     lens = [args.context] * args.batch
 
     if args.case in ("scorer", "select", "indexer"):

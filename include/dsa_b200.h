@@ -251,6 +251,19 @@ int dsa_decode_step_host(const dsa_host_step_args* args);
 int dsa_selftest_wait_expiry(uint64_t limit_ns, int32_t* status_dev, uint64_t* waited_ns_dev,
                              void* stream);
 
+/* Issue-rate measurement of the tensor-core instructions the attention kernels choose between (no
+ * counterpart in the reference; its own attempt at tcgen05 for this operator is recorded in
+ * archive/dsa_sparse_attention_h16_ckv512_kpe64_topk2048_ps64/experiments/exp_40/result.md:7-19).
+ * One CTA on all-zero shared-memory operands; nothing but the two cycle counts touches global memory.
+ *   kind 0 / 1: `iters` tcgen05.mma back to back from one thread, bf16 (m x n x 16) / e4m3
+ *               (m x n x 32), m in {64, 128}, n a multiple of 16 up to 256;
+ *               cycles_dev[0] = until the last is issued, cycles_dev[1] = until all have completed;
+ *   kind 2:     `iters` x 8 independent mma.sync.m16n8k16 per warp on `m` warps (1..32);
+ *               cycles_dev[0] = cycles_dev[1] = duration.
+ * sink_dev: one float the kernel may write (keeps the products alive). */
+int dsa_selftest_mma_rate(int kind, int m, int n, int iters, long long* cycles_dev, float* sink_dev,
+                          int32_t* status_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
