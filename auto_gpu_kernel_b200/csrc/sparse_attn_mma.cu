@@ -8,7 +8,7 @@
 // Why warp-level MMA here: with 16 heads the tcgen05 formulation has N = 16, and a tcgen05.mma costs
 // max(45.6, N/2) cycles whatever M is -- 52 instructions per 64-row tile, 3.0-4.7 k cycles, more than
 // the HBM time of the tile.  mma.sync m16n8k16 was measured on this part at 2.0 cycles per
-// instruction per SM (2048 MAC/clk); M = 16 is exactly the head count, so a tile is 544
+// instruction per SM (about 1020 MAC/clk); M = 16 is exactly the head count, so a tile is 544
 // instructions = 1.1 k cycles, and the kernel is bound by the gather as it should be.
 //
 // Structure (one CTA of 8 warps per SM, no warp specialisation, no mbarrier, nothing that spins):
