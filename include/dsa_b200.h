@@ -71,9 +71,11 @@ const char* dsa_b200_error_string(int code);
  *   topk_out     [batch,2048] int32, row stride `topk_stride` elements; receives
  *                min(2048,seq_len) global slot ids (page*64+offset) then -1
  *   workspace    >= dsa_indexer_workspace_bytes(batch,max_pages) bytes, 256-byte aligned, zero-filled
- *                once when created: two words per request (min / max of the row, left by the
- *                scorer and put back to zero by the selection; 512 KB whatever the batch), then
- *                the fp32 score rows
+ *                once when created: two words per request (min / max of the row; 512 KB whatever
+ *                the batch), then 1024 score histograms of 4096 words (16 MB whatever the batch),
+ *                then the fp32 score rows.  The scorer leaves either the row's histogram (decode
+ *                shapes up to 1024 requests) or its min / max for the selection, which puts what
+ *                it used back to zero; the histograms must be zero when a call starts
  * ------------------------------------------------------------------------------------------- */
 size_t dsa_indexer_workspace_bytes(int batch, int max_pages);
 
