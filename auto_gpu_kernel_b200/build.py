@@ -48,18 +48,33 @@ def needs_build(out: Path, csrc: Path = CSRC) -> bool:
 
 def build(out: Path | None = None, csrc: Path = CSRC, force: bool = False, verbose: bool = False,
           extra_flags=()) -> Path:
+    """Compile the library when it is missing or older than a source.  Safe when several
+    processes (one rank per GPU) call it at once: one of them compiles, into a scratch file that
+    is renamed into place, the others wait at a lock file and find the work done."""
+    import fcntl
     out = Path(out) if out else PKG_DIR / LIB_NAME
     if not force and not needs_build(out, csrc):
         return out
-    cmd = [find_nvcc(), *NVCC_FLAGS, *extra_flags]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += [str(p) for p in sources(csrc)] + ["-o", str(out)]
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose or proc.returncode != 0:
-        sys.stderr.write(proc.stdout + proc.stderr)
-    if proc.returncode != 0:
-        raise RuntimeError(f"nvcc failed ({proc.returncode}): {' '.join(cmd)}")
+    out.parent.mkdir(parents=True, exist_ok=True)
+    with open(out.with_name(out.name + ".lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not needs_build(out, csrc):
+                return out                       # another process built it while we waited
+            scratch = out.with_name(f"{out.name}.{os.getpid()}.tmp")
+            cmd = [find_nvcc(), *NVCC_FLAGS, *extra_flags]
+            if verbose:
+                cmd += ["-Xptxas", "-v"]
+            cmd += [str(p) for p in sources(csrc)] + ["-o", str(scratch)]
+            proc = subprocess.run(cmd, capture_output=True, text=True)
+            if verbose or proc.returncode != 0:
+                sys.stderr.write(proc.stdout + proc.stderr)
+            if proc.returncode != 0:
+                scratch.unlink(missing_ok=True)
+                raise RuntimeError(f"nvcc failed ({proc.returncode}): {' '.join(cmd)}")
+            os.replace(scratch, out)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return out
 
 
