@@ -124,11 +124,6 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
   if (kHist) {
     for (int i = tid; i < kHistBins; i += kTcThreads) sh.hist[i] = 0;
   }
-  ptx::grid_dependency_wait();  // q, weights, seq_lens, block_table and the cache may come from it
-  // Only now may the selection kernel be scheduled (as SMs free up; it waits for our scores): it
-  // reads seq_lens and block_table before its own wait, which is safe once OUR predecessor is done.
-  ptx::launch_dependents();
-
   // ---- tiles per request -> exclusive prefix (all threads) ------------------------------------
   {
     const int chunk = (batch + kTcThreads - 1) / kTcThreads;
@@ -172,6 +167,33 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
   const int w0 = min(total, (int)blockIdx.x * per), w1 = min(total, w0 + per);
   const uint32_t tmem_base = sh.tmem_base;
 
+  // Page ids of 32 consecutive tiles starting at w, one tile per lane (producer warp).  Both
+  // entries of a tile are requested at once (the row has max_pages entries, so the second read is
+  // in bounds); whether the second page belongs to the request is decided afterwards, so the
+  // lookup costs one round trip, not two.
+  auto lookup = [&](int w, int& bi, int& p0, int& p1, int& has2) {
+    const int wi = min(w + lane, w1 - 1);
+    bi = locate(sh.prefix, batch, wi);
+    const int ji = wi - sh.prefix[bi];
+    const int len = max(0, min(seq_lens[bi], max_pages * kPage));
+    const int n_pages = (len + kPage - 1) / kPage;
+    const int32_t* row = block_table + (size_t)bi * bt_stride + 2 * ji;
+    p0 = row[0];
+    p1 = (2 * ji + 1 < max_pages) ? row[1] : -1;
+    has2 = 2 * ji + 1 < n_pages;          // the tile has a second page
+  };
+  int first_b = 0, first_p0 = 0, first_p1 = -1, first_has2 = 0;
+  if (warp == 0 && w0 < w1) lookup(w0, first_b, first_p0, first_p1, first_has2);
+
+  // Everything above read only seq_lens and block_table, before the dependency wait (like the
+  // selection does): the kernels this library chains never write the caller's inputs, and a foreign
+  // kernel before us starts us early only if it triggers its dependents itself -- it must then not
+  // write those two afterwards.  q, weights and the cache are read after the wait.
+  ptx::grid_dependency_wait();
+  // Only now may the selection kernel be scheduled (as SMs free up; it waits for our scores): it
+  // reads seq_lens and block_table before its own wait, which is safe once OUR predecessor is done.
+  ptx::launch_dependents();
+
 #define DSA_WAIT(bar, parity)                                  \
   if (!ptx::mbar_wait(smem_u32(&(bar)), (parity))) {           \
     sh.abort_flag = 1;                                         \
@@ -182,19 +204,13 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
     if (warp == 0) {
       // ======================= producer =======================
       int stage = 0, phase = 0, qslot = 0, qphase = 0, cur_b = -1;
+      int next_b = first_b, next_p0 = first_p0, next_p1 = first_p1, next_has2 = first_has2;
       for (int w = w0; w < w1 && !sh.abort_flag; w += 32) {
-        const int wi = min(w + lane, w1 - 1);
-        const int bi = locate(sh.prefix, batch, wi);
-        const int ji = wi - sh.prefix[bi];
-        const int len = max(0, min(seq_lens[bi], max_pages * kPage));
-        const int n_pages = (len + kPage - 1) / kPage;
-        const int32_t* row = block_table + (size_t)bi * bt_stride + 2 * ji;
-        // both entries are requested at once (the row has max_pages entries, so the second read is
-        // in bounds); whether the second page belongs to the request is decided afterwards, so the
-        // lookup costs one round trip, not two
-        int p0 = row[0];
-        int p1 = (2 * ji + 1 < max_pages) ? row[1] : -1;
-        const bool has_second = 2 * ji + 1 < n_pages;
+        const int bi = next_b;
+        int p0 = next_p0, p1 = next_p1;
+        const bool has_second = next_has2 != 0;
+        // the ids of the 32 tiles after these travel while these are issued
+        if (w + 32 < w1) lookup(w + 32, next_b, next_p0, next_p1, next_has2);
         if (p0 < 0 || p0 >= num_pages) { raise_status(status, DSA_STATUS_BAD_PAGE); p0 = 0; }
         if (!has_second) {
           p1 = -1;
