@@ -129,6 +129,26 @@ def test_many_requests_complete_in_any_order(cuda, indexer_path):
         assert int(ws[: 2 * 4 * len(lens)].view(torch.int32).abs().max()) == 0
 
 
+def test_hundreds_of_medium_rows(cuda):
+    """More than two rows per SM, each small enough for half an SM's shared memory: on the min / max
+    path this is the shape that runs two narrow selection CTAs per SM (chunked prefill).  Rows with
+    600 and with 5000 tied scores at the boundary take the candidate ranking's overflow route."""
+    gen = torch.Generator().manual_seed(321)
+    lens = [int(x) for x in torch.randint(2049, 12000, (320,), generator=gen)]
+    lens[3], lens[200] = 11999, 2049
+    width = (max(lens) + 63) // 64 * 64
+    rows = torch.randn(len(lens), width, generator=gen)
+    rows[5, 1000:1600] = 0.5          # 600 ties inside the top 2048 of a ~N(0,1) row
+    rows[6, :5000] = 10.0             # 5000 ties above everything else: the lowest 2048 positions
+    rows[7] = rows[7] * 1e-6 + 3.0    # one binade
+    lens[5], lens[6], lens[7] = 9000, 9000, 9000
+    inp, got = _run(rows, lens, cuda, seed=6)
+    table = inp.block_table.cpu()
+    for b, n in enumerate(lens):
+        _check_row(rows[b], n, table[b], got[b], label=f"request {b} len {n}")
+    assert set(_local_positions(got[6], table[6], lens[6]).tolist()) == set(range(2048))
+
+
 def test_paths_select_the_same_set(cuda, monkeypatch, indexer_path):
     if indexer_path == "minmax":
         pytest.skip("compared from the other side")
