@@ -317,7 +317,8 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
         }
         return ok;
       };
-      auto flush_hist = [&](int req) -> bool {
+      // (`last`: the CTA's final flush -- the counters need not be cleared, nobody counts again)
+      auto flush_hist = [&](int req, bool last) -> bool {
         if (!group_sync()) return false;
         const int et = (warp - 2) * 32 + lane;
         uint32_t* g = ghist + (size_t)req * kHistBins;
@@ -331,16 +332,16 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
             if (cnt.y) atomicAdd(g + 4 * q + 1, cnt.y);
             if (cnt.z) atomicAdd(g + 4 * q + 2, cnt.z);
             if (cnt.w) atomicAdd(g + 4 * q + 3, cnt.w);
-            h4[q] = make_uint4(0u, 0u, 0u, 0u);
+            if (!last) h4[q] = make_uint4(0u, 0u, 0u, 0u);
           }
         }
-        return group_sync();
+        return last || group_sync();
       };
       bool alive = true;
       for (int w = w0; w < w1; ++w) {
         if (w >= next_change) {
           if (w > w0) {
-            if (kHist) { if (!flush_hist(b)) { alive = false; break; } }
+            if (kHist) { if (!flush_hist(b, false)) { alive = false; break; } }
             else flush_minmax(b);
           }
           while (sh.prefix[b + 1] <= w) ++b;
@@ -391,7 +392,7 @@ indexer_score_tc_kernel(const __grid_constant__ CUtensorMap tmap_k,
         if (++stage == kTcStages) { stage = 0; phase ^= 1; }
         if (++acc == kTcAcc) { acc = 0; aphase ^= 1; }
       }
-      if (kHist) { if (alive) flush_hist(b); }
+      if (kHist) { if (alive) flush_hist(b, true); }
       else flush_minmax(b);
     }
   }

@@ -6,8 +6,10 @@
 //   (1) boundary bin: one read of the 16 KB histogram and one block scan (every CTA of the request's
 //       cluster does it for itself, while its slice of the score row is on its way into shared memory);
 //   (2) one counting sweep over the staged slice (elements above the boundary bin, elements inside
-//       it), one block scan, one exchange of the CTAs' totals through distributed shared memory:
-//       every selected element then has its place in the output row without any atomic;
+//       it) and one block scan: every selected element then has its place in the output row without
+//       any atomic -- the row's totals are known from the histogram, so the first CTA of a pair
+//       fills the row from the front and the second from the back (a cluster of four exchanges the
+//       CTAs' totals through distributed shared memory);
 //   (3) the writing sweep; elements of the boundary bin go (key, position) into the first CTA's
 //       candidate list;
 //   (4) the first CTA picks the missing elements among the candidates exactly, by (key, lower
@@ -37,13 +39,16 @@ struct ShShared {
   int32_t table[kShTableCap];
   uint32_t sub[256];
   uint32_t warp_sums[32];
-  uint32_t edge, above, in_edge, digit, dabove, dcount, emit_cnt, carry;
+  uint32_t last[32];                    // candidates of the boundary digit, when they are few
+  uint32_t edge, above, in_edge, digit, dabove, dcount, emit_cnt, last_n;
   uint32_t peer_sel[4], peer_cnd[4];    // written by the peers
 };
 
 __device__ __forceinline__ uint32_t sh_key(float v) { return float_to_ordered(fmaxf(v, kScoreFloor)); }
 
-// Exclusive prefix sum over the CTA in thread order (three block barriers).
+// Exclusive prefix sum over the CTA in thread order (two block barriers, and a third unless the
+// caller itself passes a block or cluster barrier before warp_sums is written again).
+template <bool kTrailingBarrier = true>
 __device__ __forceinline__ uint32_t sh_block_excl_scan(uint32_t v, uint32_t* warp_sums, uint32_t* total) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   uint32_t incl = v;
@@ -66,7 +71,7 @@ __device__ __forceinline__ uint32_t sh_block_excl_scan(uint32_t v, uint32_t* war
   __syncthreads();
   const uint32_t before = warp > 0 ? warp_sums[warp - 1] : 0u;
   if (total != nullptr) *total = warp_sums[31];
-  __syncthreads();  // warp_sums may be reused by the caller
+  if (kTrailingBarrier) __syncthreads();  // warp_sums may be reused by the caller
   return before + incl - v;
 }
 
@@ -127,7 +132,11 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
   if (table_staged) {
     for (int i = tid; i < n_pages; i += kShThreads) sh.table[i] = table[i];
   }
-  if (tid == 0) { sh.in_edge = 0xFFFFFFFFu; sh.edge = 0; sh.above = 0; sh.emit_cnt = 0; }
+  if (tid == 0) {
+    sh.in_edge = 0xFFFFFFFFu; sh.edge = 0; sh.above = 0; sh.emit_cnt = 0; sh.last_n = 0;
+    sh.dcount = 0xFFFFFFFFu;
+  }
+  if (tid < 256) sh.sub[tid] = 0;   // first CTA: digit histogram of the candidates, filled as they arrive
   // The successor (the attention kernel) reads nothing before its own wait; nothing is written
   // here before ours: the output row may still be read by the kernel before us in the stream.
   ptx::launch_dependents();
@@ -163,7 +172,7 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
   }
   {
     const uint32_t mine = h.x + h.y + h.z + h.w;
-    const uint32_t excl = sh_block_excl_scan(mine, sh.warp_sums, nullptr);
+    const uint32_t excl = sh_block_excl_scan<false>(mine, sh.warp_sums, nullptr);   // barrier below
     if (excl < (uint32_t)kTopK && (uint32_t)kTopK <= excl + mine) {
       const uint32_t c[4] = {h.w, h.z, h.y, h.x};   // highest bin first
       uint32_t run = excl;
@@ -184,6 +193,11 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
     if (tid == 0 && crank == 0) raise_status(status, DSA_STATUS_TOPK_COUNT);
     return;                       // uniform over the cluster: every CTA read the same histogram
   }
+  // A cluster of one or two meets only once more (after the writing pass).  Its first CTA's digit
+  // histogram must be zero before a peer adds to it: arrive here, wait before the writing pass --
+  // by then every CTA has long arrived, so the wait costs nothing.
+  const bool exchange = csize > 2;
+  if (!exchange) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   const uint32_t need = (uint32_t)kTopK - above;   // elements wanted from the boundary bin (>= 1)
   const bool few = in_edge <= (uint32_t)kShCandCap;
   auto key_at = [&](int i) -> uint32_t { return staged ? key_s[i - seg_lo] : sh_key(__ldcg(row + i)); };
@@ -224,23 +238,40 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
     }
   }
   uint32_t totals = 0;
-  const uint32_t excl = sh_block_excl_scan(n_sel | (n_cnd << 16), sh.warp_sums, &totals);
+  const uint32_t excl = sh_block_excl_scan<false>(n_sel | (n_cnd << 16), sh.warp_sums, &totals);   // cluster barrier below
   // (a CTA holds at most 45056 staged elements, a streamed slice counts below 65536 per field only
   //  when it is shorter than that: longer streamed slices are rejected by the launcher)
-  if (tid < csize) {   // publish this CTA's totals in every CTA of the cluster
-    ShShared* peer = cluster.map_shared_rank(&sh, tid);
-    peer->peer_sel[crank] = totals & 0xFFFFu;
-    peer->peer_cnd[crank] = totals >> 16;
+  //
+  // Places in the output row and in the candidate list.  Both totals of the ROW are known from
+  // the histogram (`above`, `in_edge`), so a cluster of two needs no exchange: the first CTA fills
+  // both lists from the front, the second from the back.  A cluster of four exchanges the CTAs'
+  // totals through distributed shared memory.  In both cases the totals go to the first CTA, which
+  // checks them against the histogram once the cluster has met.
+  if (exchange) {
+    if (tid < csize) {   // publish this CTA's totals in every CTA of the cluster
+      ShShared* peer = cluster.map_shared_rank(&sh, tid);
+      peer->peer_sel[crank] = totals & 0xFFFFu;
+      peer->peer_cnd[crank] = totals >> 16;
+    }
+    cluster.sync();
+  } else {
+    if (tid == 0) {
+      ShShared* peer = cluster.map_shared_rank(&sh, 0);
+      peer->peer_sel[crank] = totals & 0xFFFFu;
+      peer->peer_cnd[crank] = totals >> 16;
+    }
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
-  cluster.sync();
-  if (crank == 0 && tid < kHistBins / 4) g4[tid] = make_uint4(0u, 0u, 0u, 0u);   // every CTA has read it
-  uint32_t sel_at = excl & 0xFFFFu, cnd_at = excl >> 16, nc = 0, sel_all = 0;
-  for (int r = 0; r < csize; ++r) {
-    if (r < crank) { sel_at += sh.peer_sel[r]; cnd_at += sh.peer_cnd[r]; }
-    nc += sh.peer_cnd[r];
-    sel_all += sh.peer_sel[r];
+  // sel_at / cnd_at: this thread's first place; `dir` +1 from the front, -1 (as unsigned) from the back
+  uint32_t sel_at = excl & 0xFFFFu, cnd_at = excl >> 16;
+  uint32_t dir = 1u;
+  if (exchange) {
+    for (int r = 0; r < crank; ++r) { sel_at += sh.peer_sel[r]; cnd_at += sh.peer_cnd[r]; }
+  } else if (crank == 1) {
+    sel_at = above - 1u - sel_at;      // wraps past zero only with inconsistent counts: the bound
+    cnd_at = in_edge - 1u - cnd_at;    // checks below then skip the write
+    dir = 0xFFFFFFFFu;
   }
-  if (crank == 0 && tid == 0 && (sel_all != above || nc != in_edge)) raise_status(status, DSA_STATUS_TOPK_COUNT);
 
   // ---- (3) writing pass: selected elements to their places, boundary bin to the candidate list ---
   ShShared* first = cluster.map_shared_rank(&sh, 0);
@@ -252,30 +283,48 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
     while (sel_mask) {
       const int bit = __ffsll((long long)sel_mask) - 1;
       sel_mask &= sel_mask - 1;
-      if (sel_at < (uint32_t)kTopK) out_row[sel_at] = slot_of(position(bit));
-      ++sel_at;
+      if (sel_at < above) out_row[sel_at] = slot_of(position(bit));
+      sel_at += dir;
     }
     while (few && cnd_mask) {
       const int bit = __ffsll((long long)cnd_mask) - 1;
       cnd_mask &= cnd_mask - 1;
       const int i = position(bit);
-      if (cnd_at < (uint32_t)kShCandCap) { first->cand_key[cnd_at] = key_s[i - seg_lo]; first->cand_idx[cnd_at] = (uint32_t)i; }
-      ++cnd_at;
+      if (cnd_at < in_edge) {
+        const uint32_t k = key_s[i - seg_lo];
+        first->cand_key[cnd_at] = k;
+        first->cand_idx[cnd_at] = (uint32_t)i;
+        atomicAdd(&first->sub[(k >> 12) & 255u], 1u);   // first pass of (4): key bits 12..19
+      }
+      cnd_at += dir;
     }
   } else {
     for (int i = seg_lo + tid; i < seg_hi; i += kShThreads) {
       const uint32_t k = key_at(i);
       if (k > hi_edge) {
-        if (sel_at < (uint32_t)kTopK) out_row[sel_at] = slot_of(i);
-        ++sel_at;
+        if (sel_at < above) out_row[sel_at] = slot_of(i);
+        sel_at += dir;
       } else if (k - lo_edge < 0x100000u) {
-        if (few && cnd_at < (uint32_t)kShCandCap) { first->cand_key[cnd_at] = k; first->cand_idx[cnd_at] = (uint32_t)i; }
-        ++cnd_at;
+        if (few && cnd_at < in_edge) {
+          first->cand_key[cnd_at] = k;
+          first->cand_idx[cnd_at] = (uint32_t)i;
+          atomicAdd(&first->sub[(k >> 12) & 255u], 1u);
+        }
+        cnd_at += dir;
       }
     }
   }
-  cluster.sync();   // candidates are in the first CTA's shared memory; the peers are done
+  cluster.sync();   // candidates and totals are in the first CTA's shared memory; the peers are done
   if (crank != 0) return;
+  if (tid < kHistBins / 4) g4[tid] = make_uint4(0u, 0u, 0u, 0u);   // every CTA of the cluster has read it
+  uint32_t nc = 0, sel_all = 0;
+  for (int r = 0; r < csize; ++r) { nc += sh.peer_cnd[r]; sel_all += sh.peer_sel[r]; }
+  if (sel_all != above || nc != in_edge) {
+    // the histogram is not this row's (junk in the workspace): the places above were not the
+    // elements' own, and candidate entries may be missing -- flag the call and leave the row
+    if (tid == 0) raise_status(status, DSA_STATUS_TOPK_COUNT);
+    return;
+  }
 
   // ---- (4) the first CTA chooses `need` elements of the boundary bin -----------------------------
   auto emit = [&](int i) {
@@ -296,14 +345,16 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
 #pragma unroll 1
       for (int pass = 0; pass < 7; ++pass) {
         const int shift = pass < 6 ? 44 - 8 * pass : 0;
-        if (tid < 256) sh.sub[tid] = 0;
-        if (tid == 0) sh.dcount = 0xFFFFFFFFu;
-        __syncthreads();
-        for (uint32_t j = tid; j < nc; j += kShThreads) {
-          const uint64_t cj = composite(j);
-          if ((cj & msk) == pfx) atomicAdd(&sh.sub[(uint32_t)(cj >> shift) & 255u], 1u);
+        if (pass > 0) {   // (the first pass's histogram was filled while the candidates arrived)
+          if (tid < 256) sh.sub[tid] = 0;
+          if (tid == 0) sh.dcount = 0xFFFFFFFFu;
+          __syncthreads();
+          for (uint32_t j = tid; j < nc; j += kShThreads) {
+            const uint64_t cj = composite(j);
+            if ((cj & msk) == pfx) atomicAdd(&sh.sub[(uint32_t)(cj >> shift) & 255u], 1u);
+          }
+          __syncthreads();
         }
-        __syncthreads();
         sh_pick_digit(sh, want);
         const uint32_t d = sh.digit, da = sh.dabove, dc = sh.dcount;
         if (dc == 0xFFFFFFFFu) {   // cannot happen with consistent counts
@@ -311,13 +362,28 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
           break;
         }
         const bool take_all = dc == want - da;
+        // A boundary digit with a handful of candidates (the usual case after one pass: a few
+        // hundred candidates over 256 digits) is settled at once: they are collected, and each
+        // ranks itself among them.
+        const bool settle = !take_all && dc <= 32u;
         for (uint32_t j = tid; j < nc; j += kShThreads) {
           const uint64_t cj = composite(j);
           if ((cj & msk) != pfx) continue;
           const uint32_t dg = (uint32_t)(cj >> shift) & 255u;
           if (dg > d || (take_all && dg == d)) emit((int)sh.cand_idx[j]);
+          else if (settle && dg == d) sh.last[atomicAdd(&sh.last_n, 1u) & 31u] = j;
         }
         if (take_all) break;
+        if (settle) {
+          __syncthreads();
+          if (tid < dc) {
+            const uint64_t cj = composite(sh.last[tid]);
+            uint32_t rank = 0;
+            for (uint32_t k = 0; k < dc; ++k) rank += composite(sh.last[k]) > cj;
+            if (rank < want - da) emit((int)sh.cand_idx[sh.last[tid]]);
+          }
+          break;
+        }
         want -= da;
         pfx |= (uint64_t)d << shift;
         msk |= 255ull << shift;
