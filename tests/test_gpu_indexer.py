@@ -196,6 +196,32 @@ def test_foreign_minmax_words_cost_speed_not_correctness(cuda, junk, monkeypatch
     assert int(words[: 2 * len(lens)].abs().sum()) == 0     # put back to zero for the next call
 
 
+def test_foreign_histogram_is_flagged_then_healed(cuda, monkeypatch):
+    """Default path (the scorer counts each request's scores into a histogram in the workspace, which
+    must be zero between calls).  Counts that are not this call's -- an aborted call, a workspace
+    that was never zeroed -- cannot be told from real ones, so the call that meets them reports
+    DSA_STATUS_TOPK_COUNT (the selection's own totals disagree with the histogram); it also puts the
+    histograms back to zero, so the next call is exact again."""
+    monkeypatch.setenv("DSA_INDEXER_PATH", "hist")
+    lens = [3000, 2049, 40000, 9000]
+    inp = wl.make_indexer_inputs(lens, seed=23, device=cuda)
+    rows = [r.cpu() for r in oracle.indexer_scores(*inp.args())]
+    first = indexer.run(*inp.args())                       # creates the shared workspace
+    workspace.check_status(cuda)
+    assert_topk_matches(inp, first, rows, label="clean")
+    ws = workspace.get(cuda, "indexer", 1)
+    hist = ws[512 * 1024: 512 * 1024 + len(lens) * 4096 * 4].view(torch.int32)
+    hist.random_(0, 5)
+    indexer.run(*inp.args())
+    with pytest.raises(RuntimeError, match="0x8"):
+        workspace.check_status(cuda)
+    torch.cuda.synchronize()
+    assert int(hist.abs().max()) == 0
+    out = indexer.run(*inp.args())
+    workspace.check_status(cuda)
+    assert_topk_matches(inp, out, rows, label="after the flagged call")
+
+
 def test_strided_block_table_and_output_rows(cuda):
     """block_table and topk_indices may be column slices of wider tensors (row stride larger than
     the row length): the reference's kernels take the strides as arguments too."""
