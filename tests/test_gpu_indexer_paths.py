@@ -149,6 +149,27 @@ def test_hundreds_of_medium_rows(cuda):
     assert set(_local_positions(got[6], table[6], lens[6]).tolist()) == set(range(2048))
 
 
+def test_more_requests_than_histograms(cuda, indexer_path):
+    """1100 requests: beyond the 1024 histograms of the workspace, so the call takes the min / max
+    selection whatever DSA_INDEXER_PATH says, and leaves the histogram region untouched."""
+    if indexer_path == "minmax":
+        pytest.skip("one run is enough: the path is chosen from the batch size")
+    gen = torch.Generator().manual_seed(1100)
+    lens = [int(x) for x in torch.randint(2049, 4000, (1100,), generator=gen)]
+    lens[0], lens[1099], lens[500] = 3999, 2049, 17
+    width = (max(lens) + 63) // 64 * 64
+    rows = torch.randn(len(lens), width, generator=gen)
+    inp, got = _run(rows, lens, cuda, seed=8)
+    table = inp.block_table.cpu()
+    for b in list(range(0, 1100, 37)) + [1023, 1024, 1099]:
+        _check_row(rows[b], lens[b], table[b], got[b], label=f"request {b} len {lens[b]}")
+    valid = (got >= 0).sum(dim=1)
+    assert torch.equal(valid, torch.tensor([min(2048, n) for n in lens]))
+    ws = workspace.get(cuda, "indexer", 1)
+    torch.cuda.synchronize()
+    assert int(ws[512 * 1024: 512 * 1024 + 1024 * 4096 * 4].view(torch.int32).abs().max()) == 0
+
+
 def test_paths_select_the_same_set(cuda, monkeypatch, indexer_path):
     if indexer_path == "minmax":
         pytest.skip("compared from the other side")
