@@ -87,6 +87,27 @@ def test_ties_take_lowest_positions(cuda):
     assert sel[2] == high | set(rest)
 
 
+@pytest.mark.parametrize("step", [0.125, 0.01])
+def test_quantised_scores_tie_across_the_boundary(cuda, step):
+    """Scores on a coarse grid: hundreds to thousands of equal values straddle the 2048th place, in
+    the boundary bin and at the exact threshold.  Equal bit patterns are taken lowest position
+    first; -0.0 ranks below +0.0 (torch.topk calls them equal, so either order is a valid top-k)."""
+    gen = torch.Generator().manual_seed(int(1 / step))
+    lens = [33000, 9000, 2049, 20000, 12345, 70000]
+    width = (max(lens) + 63) // 64 * 64
+    rows = (torch.randn(len(lens), width, generator=gen) / step).round() * step
+    inp, got = _run(rows, lens, cuda, seed=11)
+    table = inp.block_table.cpu()
+    for b, n in enumerate(lens):
+        _check_row(rows[b], n, table[b], got[b], label=f"row {b}")
+        local = _local_positions(got[b], table[b], n)
+        thr = rows[b][local].min()
+        same = (rows[b][:n].view(torch.int32) == thr.view(torch.int32)).nonzero().flatten().tolist()
+        chosen = set(local.tolist())
+        taken = [p for p in same if p in chosen]
+        assert taken == same[: len(taken)], f"row {b}: ties at the threshold are not the lowest positions"
+
+
 def test_nan_and_inf_rank_lowest(cuda):
     length = 5000
     gen = torch.Generator().manual_seed(9)
