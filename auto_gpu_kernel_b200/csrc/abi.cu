@@ -2,6 +2,7 @@
 // caller's stream.  No allocation, no synchronisation, no exceptions cross this boundary.
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 
@@ -24,6 +25,8 @@ cudaError_t launch_sparse_attn_tc(const void*, const void*, const void*, const v
                                   const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
                                   void*, int32_t*, cudaStream_t);
 size_t at_tc_workspace_bytes_auto(int tokens, int topk);
+cudaError_t launch_index_rows_exchange(int32_t* const*, uint32_t* const*, int, int, int, int, int,
+                                       int64_t, int, uint32_t, uint64_t, int32_t*, cudaStream_t);
 cudaError_t launch_sparse_attn_mma(const void*, const void*, const void*, const void*,
                                    const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
                                    void*, int32_t*, cudaStream_t);
@@ -261,6 +264,60 @@ int dsa_sparse_attn_tcgen05(const void* q_nope, const void* q_pe, const void* ck
                             int32_t* status_dev, void* stream) {
   return attn_impl(q_nope, q_pe, ckv, kpe, sparse_indices, index_stride, sm_scale, out, lse, tokens,
                    heads, topk, num_slots, workspace, workspace_bytes, status_dev, stream, 2);
+}
+
+// ---- buffers that the GPUs of one host can address in each other's memory (CUDA IPC) ----------
+int dsa_peer_slab_create(size_t bytes, void** ptr, void* handle64) {
+  if (!ptr || !handle64 || bytes == 0) return DSA_ERR_NULL_POINTER;
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return static_cast<int>(e);
+  }
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  memcpy(handle64, &h, 64);
+  *ptr = p;
+  return DSA_OK;
+}
+
+int dsa_peer_slab_open(const void* handle64, void** ptr) {
+  if (!ptr || !handle64) return DSA_ERR_NULL_POINTER;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  // opened with the CALLER's device current: peer access from it to the owner is enabled with it
+  return static_cast<int>(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+}
+
+int dsa_peer_slab_close(void* ptr) {
+  return ptr ? static_cast<int>(cudaIpcCloseMemHandle(ptr)) : DSA_OK;
+}
+
+int dsa_peer_slab_destroy(void* ptr) { return ptr ? static_cast<int>(cudaFree(ptr)) : DSA_OK; }
+
+int dsa_index_rows_exchange(int32_t* const* peer_rows, uint32_t* const* peer_ready, int world, int rank,
+                            int rows_local, int row_offset, int rows_total, int64_t row_stride,
+                            int row_width, uint32_t epoch, uint64_t wait_limit_ns,
+                            int32_t* status_dev, void* stream) {
+  if (!peer_rows || !peer_ready) return DSA_ERR_NULL_POINTER;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || rows_local < 0 || row_offset < 0 ||
+      rows_total < row_offset + rows_local || row_width <= 0 || row_width % 4 != 0 ||
+      row_stride < row_width || row_stride % 4 != 0 || wait_limit_ns == 0 ||
+      wait_limit_ns > 10000000000ull)
+    return DSA_ERR_BAD_SHAPE;
+  for (int p = 0; p < world; ++p) {
+    if (!peer_rows[p] || !peer_ready[p]) return DSA_ERR_NULL_POINTER;
+    if (!aligned16(peer_rows[p])) return DSA_ERR_MISALIGNED;
+  }
+  if (rows_total == 0) return DSA_OK;
+  return static_cast<int>(dsa::launch_index_rows_exchange(
+      peer_rows, peer_ready, world, rank, rows_local, row_offset, rows_total, row_stride, row_width,
+      epoch, wait_limit_ns, status_dev, static_cast<cudaStream_t>(stream)));
 }
 
 int dsa_index_cache_write(const void* keys, int key_dtype, int64_t key_stride, const int32_t* slots,

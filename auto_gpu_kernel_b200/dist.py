@@ -10,7 +10,9 @@ data dependencies of the two definitions:
 * head-sharded attention (`decode_block_head_sharded`): the indexer stays request-sharded, the
   attention of ALL tokens runs on every rank for that rank's 16 of the 128 heads, with the ckv/kpe
   caches replicated.  Every rank then needs every request's indices: one all-gather of the int32
-  [B, 2048] index tensor (1 MiB at B = 128) is the only exchange step of the path.
+  [B, 2048] index tensor (1 MiB at B = 128) is the only exchange step of the path
+  (`HeadShardedPlan`: NCCL), or the same exchange as pushes into the peers' buffers by a kernel
+  of this library (`PeerPushPlan`).
 
 The stage functions are parameters so that the orchestration can be exercised on CPU ranks (gloo)
 with stand-ins; by default they are the CUDA operators of this package.
@@ -83,6 +85,137 @@ class HeadShardedPlan:
             for r, c in enumerate(self.counts):
                 self.all_rows[at:at + c].copy_(self.gathered[r * self.most: r * self.most + c])
                 at += c
+        return self.all_rows
+
+
+class _DeviceBytes:
+    """A raw device allocation as an object torch can wrap without copying."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+class _PeerSlabs:
+    """One zeroed device allocation per rank that every other rank of the host can address:
+    created by the library (`dsa_peer_slab_create`), its CUDA IPC handle exchanged through the
+    process group, the peers' allocations opened with this rank's device current (which also
+    enables peer access to their GPUs).  `ptrs[r]` = rank r's slab as seen from this GPU."""
+
+    def __init__(self, nbytes: int, device, group):
+        import ctypes
+        from . import _lib, workspace
+        self._lib, self._guard, self.device = _lib, workspace.device_guard, torch.device(device)
+        lib = _lib.load()
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        own, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        with self._guard(self.device):
+            _lib.check(lib.dsa_peer_slab_create(nbytes, ctypes.addressof(own), ctypes.addressof(handle)),
+                       "dsa_peer_slab_create")
+        self.own, self.nbytes = own.value, nbytes
+        handles = [None] * world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self.ptrs, self._opened = [], []
+        for r, raw in enumerate(handles):
+            if r == rank:
+                self.ptrs.append(self.own)
+                continue
+            buf, got = ctypes.create_string_buffer(raw, 64), ctypes.c_void_p()
+            with self._guard(self.device):
+                _lib.check(lib.dsa_peer_slab_open(ctypes.addressof(buf), ctypes.addressof(got)),
+                           "dsa_peer_slab_open")
+            self.ptrs.append(got.value)
+            self._opened.append(got.value)
+        with self._guard(self.device):
+            self.tensor = torch.as_tensor(_DeviceBytes(self.own, nbytes), device=self.device)
+        self._group = group
+        dist.barrier(group=group)      # every slab is mapped everywhere before anyone writes
+
+    def close(self):
+        """Unmap the peers' slabs, then (after a barrier) free the own one."""
+        if self.own is None:
+            return
+        lib = self._lib.load()
+        self.tensor = None
+        with self._guard(self.device):
+            torch.cuda.synchronize(self.device)
+            for p in self._opened:
+                lib.dsa_peer_slab_close(p)
+            self._opened = []
+            if dist.is_initialized():
+                dist.barrier(group=self._group)
+            lib.dsa_peer_slab_destroy(self.own)
+        self.own = None
+
+
+class PeerPushPlan:
+    """Head-sharded layout without NCCL in the data path: same interface as `HeadShardedPlan`
+    (`local_rows`, `gather()`, `all_rows`), but `gather()` is one kernel of this library
+    (`dsa_index_rows_exchange`) that stores the rank's rows straight into every peer's buffer over
+    NVLink and waits, with a time limit, for the peers' rows to arrive in its own.
+
+    Every rank owns one slab -- two [B, width] int32 row buffers used alternately and B ready
+    words -- and maps its peers' slabs through CUDA IPC handles (exchanged once, through the process
+    group; `close()` releases them, collectively).  The indexer writes the rank's rows into `local_rows`, a view of the buffer the next
+    `gather()` will publish, so there is no copy on this GPU either.  One process per GPU."""
+
+    def __init__(self, counts, rank, device, group=None, width=TOPK, wait_limit_ns=5_000_000_000):
+        from . import _lib, workspace
+        self.counts = [int(c) for c in counts]
+        self.rank, self.group, self.world = rank, group, len(self.counts)
+        if self.world > 8:
+            raise ValueError("PeerPushPlan: at most 8 ranks")
+        self.total, self.width = sum(self.counts), width
+        self.offset = sum(self.counts[:rank])
+        self.device = torch.device(device)
+        self.wait_limit_ns = int(wait_limit_ns)
+        rows_bytes = self.total * width * 4
+        self._rows_bytes = rows_bytes
+        nbytes = 2 * rows_bytes + self.total * 4
+        if self.world > 1:
+            self._slabs = _PeerSlabs(nbytes, self.device, group)
+            slab, bases = self._slabs.tensor, self._slabs.ptrs
+        else:
+            self._slabs = None
+            slab = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+            bases = [slab.data_ptr()]
+        self._slab = slab
+        self._buffers = [slab[p * rows_bytes:(p + 1) * rows_bytes].view(torch.int32).view(self.total, width)
+                         for p in range(2)]
+        import ctypes
+        self._row_ptrs = [(ctypes.c_void_p * self.world)(*[b + p * rows_bytes for b in bases]) for p in range(2)]
+        self._ready_ptrs = (ctypes.c_void_p * self.world)(*[b + 2 * rows_bytes for b in bases])
+        self._ctypes = ctypes
+        self._lib, self._workspace = _lib, workspace
+        self.epoch = 0
+        self.all_rows = self._buffers[1]
+
+    def close(self):
+        """Release the shared buffers (collective: every rank calls it)."""
+        self._buffers, self._slab, self.all_rows = [], None, None
+        if self._slabs is not None:
+            self._slabs.close()
+            self._slabs = None
+
+    @property
+    def local_rows(self):
+        """The rank's rows inside the buffer that the next `gather()` publishes."""
+        buf = self._buffers[(self.epoch + 1) & 1]
+        return buf[self.offset: self.offset + self.counts[self.rank]]
+
+    def gather(self):
+        self.epoch += 1
+        parity = self.epoch & 1
+        lib = self._lib.load()
+        with self._workspace.device_guard(self.device):
+            rc = lib.dsa_index_rows_exchange(
+                self._ctypes.addressof(self._row_ptrs[parity]), self._ctypes.addressof(self._ready_ptrs),
+                self.world, self.rank, self.counts[self.rank], self.offset, self.total, self.width,
+                self.width, self.epoch & 0xFFFFFFFF, self.wait_limit_ns,
+                self._workspace.status_word(self.device).data_ptr(),
+                self._workspace.stream_handle(self.device))
+        self._lib.check(rc, "dsa_index_rows_exchange")
+        self.all_rows = self._buffers[parity]
         return self.all_rows
 
 

@@ -244,6 +244,38 @@ typedef struct dsa_host_step_args {
 
 int dsa_decode_step_host(const dsa_host_step_args* args);
 
+/* Device buffers that the other GPUs of the host can address (no counterpart in the reference).
+ * The library allocates nothing on its own; these four calls are the explicit exception, made by
+ * the caller once when a head-sharded layer is set up.  `create` allocates `bytes` of zeroed device
+ * memory on the current device and writes its 64-byte CUDA IPC handle to `handle64`; the handle
+ * travels to the peer processes by whatever channel the caller has; `open`, made there with the
+ * peer's own device current, returns the address of that memory as seen from it (peer access to the
+ * owner is enabled with it); `close` unmaps it; `destroy` frees the owner's memory, after every peer
+ * has closed it.  One process per GPU.  Return values as everywhere: 0, DSA_ERR_*, or cudaError_t. */
+int dsa_peer_slab_create(size_t bytes, void** ptr, void* handle64);
+int dsa_peer_slab_open(const void* handle64, void** ptr);
+int dsa_peer_slab_close(void* ptr);
+int dsa_peer_slab_destroy(void* ptr);
+
+/* Exchange of index rows between the GPUs of a head-sharded layer (no counterpart in the reference,
+ * which is single-GPU: its operators meet only through the index tensor, indexer_baseline.py:82-90 ->
+ * sparse_baseline.py:22-28).  Every rank owns one buffer `rows[rows_total][row_stride]` int32 and
+ * one array `ready[rows_total]` uint32 (zero when created) that its peers can address;
+ * `peer_rows[p]` / `peer_ready[p]` (HOST arrays of `world` device pointers, entry `rank` being the
+ * caller's own) are those buffers as seen from this GPU.  The call copies the caller's local rows
+ * [row_offset, row_offset + rows_local) -- already in its own buffer, `row_width` ids each -- into
+ * the same rows of every peer's buffer with plain stores, then stores `epoch` into those rows' ready
+ * words on every peer, then waits until every other row of its OWN ready array holds `epoch` or a
+ * later value.  When the kernel has completed, rows_total rows are in the caller's own buffer.
+ * `epoch` must grow by one per call on every rank (start at 1); two row buffers used alternately
+ * (by the epoch's parity) keep a rank that runs ahead from overwriting rows a peer still reads.
+ * The wait ends after `wait_limit_ns` (1 .. 1e10) with DSA_STATUS_WAIT_TIMEOUT in *status_dev; the
+ * context stays usable.  One process per GPU; never run two ranks on one GPU. */
+int dsa_index_rows_exchange(int32_t* const* peer_rows, uint32_t* const* peer_ready, int world, int rank,
+                            int rows_local, int row_offset, int rows_total, int64_t row_stride,
+                            int row_width, uint32_t epoch, uint64_t wait_limit_ns,
+                            int32_t* status_dev, void* stream);
+
 /* Self-test of the bounded device-side waits (no counterpart in the reference, whose kernels spin
  * without a limit: sparse_fused.py:135-137).  One thread waits for at most `limit_ns` nanoseconds
  * (1 .. 1e9) on a barrier that receives no arrival, then sets DSA_STATUS_WAIT_TIMEOUT in

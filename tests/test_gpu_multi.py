@@ -62,6 +62,110 @@ def _worker(rank, world, port, result_path):
         dist.destroy_process_group()
 
 
+def _push_worker(rank, world, port, result_path):
+    """Head-sharded block with the index rows pushed by the library's own exchange kernel, three steps
+    with changing inputs (both row buffers and growing epochs), ragged shards."""
+    for p in (ROOT, ROOT / "oracle"):
+        if str(p) not in sys.path:
+            sys.path.insert(0, str(p))
+    import torch.distributed as dist
+    from auto_gpu_kernel_b200 import dist as dsa_dist, indexer, inputs as wl, sparse_attention, workspace
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        lens = [3000, 2100, 70, 5000, 2500, 4097, 9000]
+        batch = len(lens)
+        counts = [len(dsa_dist.shard_range(batch, r, world)) for r in range(world)]
+        mine = dsa_dist.shard_range(batch, rank, world)
+        sel = slice(mine.start, mine.stop)
+        plan = dsa_dist.PeerPushPlan(counts, rank, dev)
+        heads = slice(16 * rank, 16 * rank + 16)
+        ok = True
+        for step in range(3):
+            block = wl.make_decode_block_inputs(lens, seed=20 + step, device=dev, heads=16 * world)
+            idx = block.indexer
+            local_args = (idx.q_index_fp8[sel].contiguous(), idx.k_index_cache_fp8,
+                          idx.weights[sel].contiguous(), idx.seq_lens[sel].contiguous(),
+                          idx.block_table[sel].contiguous())
+            qn, qp = block.q_nope[:, heads].contiguous(), block.q_pe[:, heads].contiguous()
+            out = torch.empty(batch, 16, 512, dtype=torch.bfloat16, device=dev)
+            lse = torch.empty(batch, 16, dtype=torch.float32, device=dev)
+            gathered = dsa_dist.decode_block_head_sharded(local_args, counts, qn, qp, block.ckv_cache,
+                                                          block.kpe_cache, block.sm_scale, out, lse, plan=plan)
+            workspace.check_status(dev)
+            want_idx = indexer.run(*idx.args())
+            want_out, want_lse = sparse_attention.run(qn, qp, block.ckv_cache, block.kpe_cache, gathered,
+                                                      block.sm_scale)
+            ok = ok and torch.equal(torch.sort(gathered, 1).values, torch.sort(want_idx, 1).values)
+            ok = ok and torch.equal(out.view(torch.int16), want_out.view(torch.int16)) and torch.equal(lse, want_lse)
+            ok = ok and plan.epoch == step + 1
+        plan.close()
+        flags = [None] * world
+        dist.all_gather_object(flags, bool(ok))
+        if rank == 0:
+            Path(result_path).write_text("ok" if all(flags) else f"mismatch {flags}")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_head_sharded_block_with_pushed_rows_on_two_gpus(tmp_path):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    result = tmp_path / "result.txt"
+    mp.spawn(_push_worker, args=(2, _free_port(), str(result)), nprocs=2, join=True)
+    assert result.read_text() == "ok"
+
+
+def test_row_exchange_two_ranks_in_turn_on_one_gpu(cuda):
+    """The exchange kernel with both ranks' buffers on one GPU, the ranks called one after the other
+    (never at the same time): rank 1 pushes and, with rank 0 silent, its wait runs out after the
+    2 ms it was given and reports DSA_STATUS_WAIT_TIMEOUT; rank 0 then pushes and finds rank 1's rows
+    already there.  Afterwards both buffers hold all rows."""
+    import ctypes
+    for p in (ROOT, ROOT / "oracle"):
+        if str(p) not in sys.path:
+            sys.path.insert(0, str(p))
+    from auto_gpu_kernel_b200 import _lib, workspace
+    lib = _lib.load()
+    counts, width = [5, 3], 2048
+    total = sum(counts)
+    gen = torch.Generator(device=cuda).manual_seed(5)
+    truth = torch.randint(0, 1 << 20, (total, width), dtype=torch.int32, device=cuda, generator=gen)
+    rows = [torch.full((total, width), -7, dtype=torch.int32, device=cuda) for _ in range(2)]
+    ready = [torch.zeros(total, dtype=torch.int32, device=cuda) for _ in range(2)]
+    rows[0][:5] = truth[:5]
+    rows[1][5:] = truth[5:]
+    row_ptrs = (ctypes.c_void_p * 2)(rows[0].data_ptr(), rows[1].data_ptr())
+    ready_ptrs = (ctypes.c_void_p * 2)(ready[0].data_ptr(), ready[1].data_ptr())
+    status = workspace.status_word(cuda)
+
+    def call(rank, limit_ns):
+        offset = sum(counts[:rank])
+        rc = lib.dsa_index_rows_exchange(ctypes.addressof(row_ptrs), ctypes.addressof(ready_ptrs), 2, rank,
+                                         counts[rank], offset, total, width, width, 1, limit_ns,
+                                         status.data_ptr(), workspace.stream_handle(cuda))
+        _lib.check(rc, "dsa_index_rows_exchange")
+
+    call(1, 2_000_000)
+    with pytest.raises(RuntimeError, match="0x1"):
+        workspace.check_status(cuda)
+    assert torch.equal(rows[0][5:], truth[5:]) and (ready[0][5:] == 1).all() and (ready[0][:5] == 0).all()
+    call(0, 2_000_000)
+    assert workspace.check_status(cuda) == 0
+    assert torch.equal(rows[0], truth) and torch.equal(rows[1], truth)
+    assert (ready[0] == 1).all() and (ready[1] == 1).all()
+    # argument checks
+    assert lib.dsa_index_rows_exchange(ctypes.addressof(row_ptrs), ctypes.addressof(ready_ptrs), 9, 0, 1, 0, 8,
+                                       width, width, 1, 1000, status.data_ptr(), None) < 0
+    assert lib.dsa_index_rows_exchange(ctypes.addressof(row_ptrs), ctypes.addressof(ready_ptrs), 2, 0, 5, 0, 8,
+                                       width, width, 1, 0, status.data_ptr(), None) < 0
+
+
 def test_head_sharded_block_on_two_gpus(tmp_path):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
