@@ -25,8 +25,8 @@ cudaError_t launch_sparse_attn_tc(const void*, const void*, const void*, const v
                                   const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
                                   void*, int32_t*, cudaStream_t);
 size_t at_tc_workspace_bytes_auto(int tokens, int topk);
-cudaError_t launch_index_rows_exchange(int32_t* const*, uint32_t* const*, int, int, int, int, int,
-                                       int64_t, int, uint32_t, uint64_t, int32_t*, cudaStream_t);
+cudaError_t launch_index_rows_exchange(int32_t*, uint2* const*, int, int, int, int, int, int64_t, int,
+                                       uint32_t, uint64_t, int32_t*, cudaStream_t);
 cudaError_t launch_sparse_attn_mma(const void*, const void*, const void*, const void*,
                                    const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
                                    void*, int32_t*, cudaStream_t);
@@ -300,24 +300,26 @@ int dsa_peer_slab_close(void* ptr) {
 
 int dsa_peer_slab_destroy(void* ptr) { return ptr ? static_cast<int>(cudaFree(ptr)) : DSA_OK; }
 
-int dsa_index_rows_exchange(int32_t* const* peer_rows, uint32_t* const* peer_ready, int world, int rank,
-                            int rows_local, int row_offset, int rows_total, int64_t row_stride,
-                            int row_width, uint32_t epoch, uint64_t wait_limit_ns,
-                            int32_t* status_dev, void* stream) {
-  if (!peer_rows || !peer_ready) return DSA_ERR_NULL_POINTER;
+int dsa_index_rows_exchange(int32_t* rows, void* const* peer_stage, int world, int rank, int rows_local,
+                            int row_offset, int rows_total, int64_t row_stride, int row_width,
+                            uint32_t epoch, uint64_t wait_limit_ns, int32_t* status_dev, void* stream) {
+  if (!rows || !peer_stage) return DSA_ERR_NULL_POINTER;
   if (world < 1 || world > 8 || rank < 0 || rank >= world || rows_local < 0 || row_offset < 0 ||
-      rows_total < row_offset + rows_local || row_width <= 0 || row_width % 4 != 0 ||
-      row_stride < row_width || row_stride % 4 != 0 || wait_limit_ns == 0 ||
+      rows_total < row_offset + rows_local || row_width <= 0 || row_width % 2 != 0 ||
+      row_stride < row_width || row_stride % 2 != 0 || epoch == 0 || wait_limit_ns == 0 ||
       wait_limit_ns > 10000000000ull)
     return DSA_ERR_BAD_SHAPE;
+  if (reinterpret_cast<uintptr_t>(rows) & 7u) return DSA_ERR_MISALIGNED;
+  uint2* stage[8] = {};
   for (int p = 0; p < world; ++p) {
-    if (!peer_rows[p] || !peer_ready[p]) return DSA_ERR_NULL_POINTER;
-    if (!aligned16(peer_rows[p])) return DSA_ERR_MISALIGNED;
+    if (!peer_stage[p]) return DSA_ERR_NULL_POINTER;
+    if (!aligned16(peer_stage[p])) return DSA_ERR_MISALIGNED;
+    stage[p] = static_cast<uint2*>(peer_stage[p]);
   }
   if (rows_total == 0) return DSA_OK;
   return static_cast<int>(dsa::launch_index_rows_exchange(
-      peer_rows, peer_ready, world, rank, rows_local, row_offset, rows_total, row_stride, row_width,
-      epoch, wait_limit_ns, status_dev, static_cast<cudaStream_t>(stream)));
+      rows, stage, world, rank, rows_local, row_offset, rows_total, row_stride, row_width, epoch,
+      wait_limit_ns, status_dev, static_cast<cudaStream_t>(stream)));
 }
 
 int dsa_index_cache_write(const void* keys, int key_dtype, int64_t key_stride, const int32_t* slots,

@@ -3,15 +3,18 @@
 // In the head-sharded layout every rank runs the indexer for its own requests and the attention
 // of ALL requests for its own heads, so each rank needs every rank's int32 [rows, 2048] index rows
 // (the reference has no multi-GPU code; its two operators meet only through this tensor:
-// indexer_baseline.py:82-90 -> sparse_baseline.py:22-28).  Here the producer pushes: one CTA per
-// local row copies the row (8 KB) into the same place of every peer's buffer with plain 16-byte
-// stores over NVLink, fences, and stores the call's epoch into the row's ready word on that peer.
-// The same kernel then waits, one thread per row, until every remote row of its own buffer carries
-// this epoch (or a later one) -- a wait with a time limit that ends in DSA_STATUS_WAIT_TIMEOUT --
-// so that the attention kernel behind it in the stream finds the whole tensor in local memory.
+// indexer_baseline.py:82-90 -> sparse_baseline.py:22-28).  One kernel per rank and step does both
+// directions with no fence and no separate flag:
+//   * push: the CTA of a LOCAL row reads it from the rank's own index tensor and stores it into the
+//     row's place of every peer's staging buffer as (id, epoch) pairs -- 16-byte stores of two
+//     pairs over NVLink, each 8-byte pair written whole;
+//   * take: the CTA of a REMOTE row polls that row of its OWN staging buffer until every pair
+//     carries this call's epoch, and writes the ids into the rank's index tensor.
+// A pair that carries the epoch is its own proof of arrival, so the latency is one NVLink trip
+// instead of data + fence + flag.  The poll has a time limit that ends in DSA_STATUS_WAIT_TIMEOUT.
 // Nothing is ever read from a peer's memory, and nothing on this GPU waits for another kernel of
-// this GPU.  Buffers alternate with the epoch's parity on the host side: a rank can run at most one
-// step ahead of a peer's attention, so it never overwrites rows that are still being read.
+// this GPU.  The host alternates two staging buffers with the epoch's parity: a rank can run at
+// most one step ahead of a peer's take, so it never overwrites pairs that are still being read.
 #include "common.cuh"
 #include "ptx.cuh"
 #include "tmap.cuh"
@@ -22,81 +25,76 @@ constexpr int kXchThreads = 256;
 constexpr int kXchMaxWorld = 8;
 
 struct XchPeers {
-  int32_t* rows[kXchMaxWorld];    // every rank's [rows_total, row_stride] buffer (own one included)
-  uint32_t* ready[kXchMaxWorld];  // every rank's [rows_total] ready words
+  uint2* stage[kXchMaxWorld];   // every rank's [rows_total][row_width] (id, epoch) staging buffer
 };
 
 namespace {
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }
 
 __global__ void __launch_bounds__(kXchThreads)
-index_rows_exchange_kernel(XchPeers peers, int world, int rank, int rows_local, int row_offset,
-                           int rows_total, int64_t row_stride, int row_width, uint32_t epoch,
-                           uint64_t limit_ns, int32_t* status) {
+index_rows_exchange_kernel(int32_t* __restrict__ rows, XchPeers peers, int world, int rank,
+                           int rows_local, int row_offset, int rows_total, int64_t row_stride,
+                           int row_width, uint32_t epoch, uint64_t limit_ns, int32_t* status) {
   const int tid = threadIdx.x;
   // the local rows come from the selection kernel before us in the stream
   ptx::grid_dependency_wait();
   ptx::launch_dependents();   // the attention behind us waits for this whole kernel by itself
-
-  // ---- push: CTA b owns local row b ----
+  const int pairs2 = row_width / 2;   // 16-byte units (two pairs) per row
+  // ---- push: local row b by CTA b, b + grid, ... (before any take: a CTA never polls while it
+  //      still has rows to send) ----
   for (int b = blockIdx.x; b < rows_local; b += gridDim.x) {
-    const size_t row_at = (size_t)(row_offset + b) * row_stride;
-    const uint4* src = reinterpret_cast<const uint4*>(peers.rows[rank] + row_at);
-    const int chunks = row_width / 4;   // 16-byte chunks per row
-    for (int c = tid; c < chunks; c += kXchThreads) {
-      const uint4 v = __ldcg(src + c);
+    const int i = row_offset + b;
+    const int32_t* row = rows + (size_t)i * row_stride;
+    for (int u = tid; u < pairs2; u += kXchThreads) {
+      const int2 v = __ldcg(reinterpret_cast<const int2*>(row) + u);
+      const uint4 packed = make_uint4((uint32_t)v.x, epoch, (uint32_t)v.y, epoch);
       for (int p = 0; p < world; ++p) {
         if (p == rank) continue;
-        reinterpret_cast<uint4*>(peers.rows[p] + row_at)[c] = v;
+        reinterpret_cast<uint4*>(peers.stage[p] + (size_t)i * row_width)[u] = packed;
       }
     }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < world && tid != rank) st_release_sys(peers.ready[tid] + row_offset + b, epoch);
-    if (tid == 0) st_release_sys(peers.ready[rank] + row_offset + b, epoch);
   }
-
-  // ---- wait: one thread per row of the whole tensor ----
-  for (int i = blockIdx.x * kXchThreads + tid; i < rows_total; i += gridDim.x * kXchThreads) {
-    if (i >= row_offset && i < row_offset + rows_local) continue;   // own rows: stream order
-    const uint32_t* word = peers.ready[rank] + i;
-    bool ok = (int32_t)(ld_acquire_sys(word) - epoch) >= 0;
-    if (!ok) {
-      const uint64_t t0 = ptx::global_timer_ns();
-      for (uint32_t spins = 0; !ok; ++spins) {
-        ok = (int32_t)(ld_acquire_sys(word) - epoch) >= 0;
-        if (!ok && (spins & 15u) == 15u) {
-          if (ptx::global_timer_ns() - t0 > limit_ns) break;
-          __nanosleep(200);
+  // ---- take: the k-th remote row by CTA k, k + grid, ... ----
+  const int rows_remote = rows_total - rows_local;
+  for (int k = blockIdx.x; k < rows_remote; k += gridDim.x) {
+    const int i = k < row_offset ? k : k + rows_local;
+    int32_t* row = rows + (size_t)i * row_stride;
+    const uint4* src = reinterpret_cast<const uint4*>(peers.stage[rank] + (size_t)i * row_width);
+    uint64_t t0 = 0;
+    bool gave_up = false;
+    for (int u = tid; u < pairs2; u += kXchThreads) {
+      uint4 v = ld_volatile_v4(src + u);
+      for (uint32_t spins = 0; !gave_up && (v.y != epoch || v.w != epoch); ++spins) {
+        if ((spins & 31u) == 31u) {
+          const uint64_t now = ptx::global_timer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > limit_ns) gave_up = true;
         }
+        v = ld_volatile_v4(src + u);
       }
+      if (gave_up) break;
+      reinterpret_cast<int2*>(row)[u] = make_int2((int32_t)v.x, (int32_t)v.z);
     }
-    if (!ok) raise_status(status, DSA_STATUS_WAIT_TIMEOUT);
+    if (gave_up) raise_status(status, DSA_STATUS_WAIT_TIMEOUT);
   }
 }
 
 }  // namespace
 
-cudaError_t launch_index_rows_exchange(int32_t* const* peer_rows, uint32_t* const* peer_ready, int world,
-                                       int rank, int rows_local, int row_offset, int rows_total,
-                                       int64_t row_stride, int row_width, uint32_t epoch,
-                                       uint64_t limit_ns, int32_t* status, cudaStream_t stream) {
+cudaError_t launch_index_rows_exchange(int32_t* rows, uint2* const* peer_stage, int world, int rank,
+                                       int rows_local, int row_offset, int rows_total, int64_t row_stride,
+                                       int row_width, uint32_t epoch, uint64_t limit_ns, int32_t* status,
+                                       cudaStream_t stream) {
   XchPeers peers = {};
-  for (int p = 0; p < world; ++p) {
-    peers.rows[p] = peer_rows[p];
-    peers.ready[p] = peer_ready[p];
-  }
-  const int wait_ctas = (rows_total + kXchThreads - 1) / kXchThreads;
+  for (int p = 0; p < world; ++p) peers.stage[p] = peer_stage[p];
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)max(1, max(rows_local, wait_ctas)));
+  cfg.gridDim = dim3((unsigned)min(max(rows_total, 1), 1024));
   cfg.blockDim = dim3(kXchThreads);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -104,8 +102,8 @@ cudaError_t launch_index_rows_exchange(int32_t* const* peer_rows, uint32_t* cons
   attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled();
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, index_rows_exchange_kernel, peers, world, rank, rows_local, row_offset,
-                            rows_total, row_stride, row_width, epoch, limit_ns, status);
+  return cudaLaunchKernelEx(&cfg, index_rows_exchange_kernel, rows, peers, world, rank, rows_local,
+                            row_offset, rows_total, row_stride, row_width, epoch, limit_ns, status);
 }
 
 }  // namespace dsa

@@ -151,15 +151,18 @@ class _PeerSlabs:
 class PeerPushPlan:
     """Head-sharded layout without NCCL in the data path: same interface as `HeadShardedPlan`
     (`local_rows`, `gather()`, `all_rows`), but `gather()` is one kernel of this library
-    (`dsa_index_rows_exchange`) that stores the rank's rows straight into every peer's buffer over
-    NVLink and waits, with a time limit, for the peers' rows to arrive in its own.
+    (`dsa_index_rows_exchange`) that stores the rank's rows as (id, epoch) pairs straight into
+    every peer's staging buffer over NVLink and takes the peers' rows out of its own as soon as
+    their pairs carry the step's epoch (a poll with a time limit).
 
-    Every rank owns one slab -- two [B, width] int32 row buffers used alternately and B ready
-    words -- and maps its peers' slabs through CUDA IPC handles (exchanged once, through the process
-    group; `close()` releases them, collectively).  The indexer writes the rank's rows into `local_rows`, a view of the buffer the next
-    `gather()` will publish, so there is no copy on this GPU either.  One process per GPU."""
+    Every rank owns one slab -- two staging buffers of B x width pairs, used alternately -- and maps
+    its peers' slabs through CUDA IPC handles (exchanged once, through the process group; `close()`
+    releases them, collectively).  The index tensor itself is ordinary device memory: the indexer
+    writes the rank's rows into `local_rows`, a view of it, and the attention reads `all_rows`, the
+    whole of it, so there is no copy on this GPU either.  One process per GPU."""
 
     def __init__(self, counts, rank, device, group=None, width=TOPK, wait_limit_ns=5_000_000_000):
+        import ctypes
         from . import _lib, workspace
         self.counts = [int(c) for c in counts]
         self.rank, self.group, self.world = rank, group, len(self.counts)
@@ -169,53 +172,38 @@ class PeerPushPlan:
         self.offset = sum(self.counts[:rank])
         self.device = torch.device(device)
         self.wait_limit_ns = int(wait_limit_ns)
-        rows_bytes = self.total * width * 4
-        self._rows_bytes = rows_bytes
-        nbytes = 2 * rows_bytes + self.total * 4
+        self.all_rows = torch.full((self.total, width), -1, dtype=torch.int32, device=self.device)
+        self.local_rows = self.all_rows[self.offset: self.offset + self.counts[rank]]
+        stage_bytes = self.total * width * 8
         if self.world > 1:
-            self._slabs = _PeerSlabs(nbytes, self.device, group)
-            slab, bases = self._slabs.tensor, self._slabs.ptrs
+            self._slabs = _PeerSlabs(2 * stage_bytes, self.device, group)
+            bases = self._slabs.ptrs
         else:
             self._slabs = None
-            slab = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
-            bases = [slab.data_ptr()]
-        self._slab = slab
-        self._buffers = [slab[p * rows_bytes:(p + 1) * rows_bytes].view(torch.int32).view(self.total, width)
-                         for p in range(2)]
-        import ctypes
-        self._row_ptrs = [(ctypes.c_void_p * self.world)(*[b + p * rows_bytes for b in bases]) for p in range(2)]
-        self._ready_ptrs = (ctypes.c_void_p * self.world)(*[b + 2 * rows_bytes for b in bases])
+            self._own = torch.zeros(2 * stage_bytes, dtype=torch.uint8, device=self.device)
+            bases = [self._own.data_ptr()]
+        self._stage_ptrs = [(ctypes.c_void_p * self.world)(*[b + p * stage_bytes for b in bases]) for p in range(2)]
         self._ctypes = ctypes
         self._lib, self._workspace = _lib, workspace
         self.epoch = 0
-        self.all_rows = self._buffers[1]
 
     def close(self):
         """Release the shared buffers (collective: every rank calls it)."""
-        self._buffers, self._slab, self.all_rows = [], None, None
         if self._slabs is not None:
             self._slabs.close()
             self._slabs = None
 
-    @property
-    def local_rows(self):
-        """The rank's rows inside the buffer that the next `gather()` publishes."""
-        buf = self._buffers[(self.epoch + 1) & 1]
-        return buf[self.offset: self.offset + self.counts[self.rank]]
-
     def gather(self):
         self.epoch += 1
-        parity = self.epoch & 1
         lib = self._lib.load()
         with self._workspace.device_guard(self.device):
             rc = lib.dsa_index_rows_exchange(
-                self._ctypes.addressof(self._row_ptrs[parity]), self._ctypes.addressof(self._ready_ptrs),
-                self.world, self.rank, self.counts[self.rank], self.offset, self.total, self.width,
-                self.width, self.epoch & 0xFFFFFFFF, self.wait_limit_ns,
-                self._workspace.status_word(self.device).data_ptr(),
+                self.all_rows.data_ptr(), self._ctypes.addressof(self._stage_ptrs[self.epoch & 1]),
+                self.world, self.rank, self.counts[self.rank], self.offset, self.total,
+                self.all_rows.stride(0), self.width, ((self.epoch - 1) % 0xFFFFFFFF) + 1,
+                self.wait_limit_ns, self._workspace.status_word(self.device).data_ptr(),
                 self._workspace.stream_handle(self.device))
         self._lib.check(rc, "dsa_index_rows_exchange")
-        self.all_rows = self._buffers[parity]
         return self.all_rows
 
 

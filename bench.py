@@ -182,14 +182,18 @@ def timed_us(step, steps, warmup, ranks, sampler=None):
     return e0.elapsed_time(e1) * 1e3 / steps
 
 
-def sample_clocks(step, sampler):
+def sample_clocks(step, sampler, batches=None):
     """The timed region lasts milliseconds, less than nvidia-smi's sampling period: keep the very
-    same steps running for 1.2 s so that the clock samples are taken under this load."""
+    same steps running for 1.2 s so that the clock samples are taken under this load.  A step that
+    holds an exchange between ranks is repeated `batches` x 20 times instead, the same count on
+    every rank."""
     t0 = time.perf_counter()
-    while time.perf_counter() - t0 < 1.2:
+    done = 0
+    while (time.perf_counter() - t0 < 1.2) if batches is None else (done < batches):
         for _ in range(20):
             step()
         torch.cuda.synchronize()
+        done += 1
     clocks = sampler.stop()
     clocks["window"] = "timed steps, then the same steps repeated for 1.2 s"
     return clocks
@@ -385,18 +389,31 @@ def head_sharded_setup(ranks, batch=128, lo=16384, hi=65536):
     out = torch.empty(batch, 16, 512, dtype=torch.bfloat16, device=dev)
     lse = torch.empty(batch, 16, dtype=torch.float32, device=dev)
 
-    def step():
-        dsa_dist.decode_block_head_sharded(local_args, counts, q_nope, q_pe, block.ckv_cache,
-                                           block.kpe_cache, block.sm_scale, out, lse, plan=plan)
+    def make_step(p):
+        def step():
+            dsa_dist.decode_block_head_sharded(local_args, counts, q_nope, q_pe, block.ckv_cache,
+                                               block.kpe_cache, block.sm_scale, out, lse, plan=p)
+        return step
 
     def gather_only():
         plan.gather()
 
+    # the same exchange as pushes into the peers' buffers by the library's own kernel (no NCCL in
+    # the data path); set up collectively, so a failure is the same on every rank
+    push_plan, push_error = None, None
+    if world > 1:
+        try:
+            push_plan = dsa_dist.PeerPushPlan(counts, rank, dev)
+        except Exception as exc:   # noqa: BLE001 - reported in the JSON line
+            push_error = f"{type(exc).__name__}: {exc}"[:200]
     my_tokens = sum(lens[i] for i in mine)
-    return step, gather_only, {"requests_on_rank0": len(mine), "cached_tokens_on_rank0": my_tokens,
-                               "lens": lens, "local_args": local_args,
-                               "attention": (q_nope, q_pe, block.ckv_cache, block.kpe_cache, block.sm_scale),
-                               "out": out, "lse": lse, "plan": plan}
+    return make_step(plan), gather_only, {"requests_on_rank0": len(mine), "cached_tokens_on_rank0": my_tokens,
+                                          "lens": lens, "local_args": local_args,
+                                          "attention": (q_nope, q_pe, block.ckv_cache, block.kpe_cache, block.sm_scale),
+                                          "out": out, "lse": lse, "plan": plan, "push_plan": push_plan,
+                                          "push_error": push_error,
+                                          "push_step": make_step(push_plan) if push_plan is not None else None,
+                                          "push_only": push_plan.gather if push_plan is not None else None}
 
 
 def cfg2_setup(ranks, batch=256, lo=32768, hi=131072):
@@ -626,12 +643,17 @@ def run_headline(args, ranks):
         hs_step, gather_only, info = head_sharded_setup(ranks)
         hs_us = timed_us(hs_step, args.steps, args.warmup, ranks)
         ag_us = timed_us(gather_only, args.steps, args.warmup, ranks)
+        hsp_us = timed_us(info["push_step"], args.steps, args.warmup, ranks) if info["push_step"] else 0.0
+        push_us = timed_us(info["push_only"], args.steps, args.warmup, ranks) if info["push_only"] else 0.0
+        workspace.check_status(dev)
+        if info["push_plan"] is not None:
+            info["push_plan"].close()
         del hs_step, gather_only, info
         torch.cuda.empty_cache()
         c2_step, c2_lens, _, _, _ = cfg2_setup(ranks)
         c2_us = timed_us(c2_step, max(5, args.steps // 2), args.warmup, ranks)
-        extra_keys = ["head_sharded_us", "allgather_us", "cfg2_us"]
-        extra_vals = [hs_us, ag_us, c2_us]
+        extra_keys = ["head_sharded_us", "allgather_us", "head_sharded_push_us", "push_us", "cfg2_us"]
+        extra_vals = [hs_us, ag_us, hsp_us, push_us, c2_us]
         workspace.check_status(dev)
 
     vals = ranks.max_over_ranks([step_us, e2e, idx_us, att_us, score_us, idx_sep_us, att_sep_us] + extra_vals)
@@ -655,7 +677,10 @@ def run_headline(args, ranks):
     for k, v in zip(extra_keys, vals[7:]):
         stages[k] = v
     if extra_keys:
-        stages["head_sharded"] = "cfg4: B=128 ctx~U[16K,64K], indexer request-sharded, all_gather of int32 [128,2048], attention 16 heads/GPU"
+        stages["head_sharded"] = ("cfg4: B=128 ctx~U[16K,64K], indexer request-sharded, int32 [128,2048] index rows "
+                                  "exchanged, attention 16 heads/GPU; head_sharded_us / allgather_us with the NCCL "
+                                  "all_gather, head_sharded_push_us / push_us with the library's own exchange kernel "
+                                  "(0 = could not be set up)")
         stages["cfg2"] = f"B=256 ctx~U[32K,128K], {256 // world} requests per GPU (strong scaling)"
     line = {
         "metric": w.metric, "value": step_us, "unit": "us", "n_gpus": world, "steps": args.steps,
@@ -837,18 +862,29 @@ def run_cfg3(args, ranks):
 
 def run_cfg4(args, ranks):
     from auto_gpu_kernel_b200 import indexer, sparse_attention, workspace
-    step, gather_only, info = head_sharded_setup(ranks)
+    nccl_step, gather_only, info = head_sharded_setup(ranks)
+    push_step, push_only = info["push_step"], info["push_only"]
+    # the layer as the library runs it: index rows pushed by its own kernel where that could be
+    # set up, otherwise (and always at one GPU) the NCCL all-gather
+    step = push_step if push_step is not None else nccl_step
     sampler = ClockSampler(ranks.local)
     us = timed_us(step, args.steps, args.warmup, ranks, sampler)
-    clocks = sample_clocks(step, sampler)
+    (us_all,) = ranks.max_over_ranks([us])
+    batches = None if ranks.world == 1 else max(1, int(1.2e6 / (20.0 * max(us_all, 1.0))))
+    clocks = sample_clocks(step, sampler, batches)
     workspace.check_status(ranks.dev)
+    nccl_us = timed_us(nccl_step, args.steps, args.warmup, ranks) if push_step is not None else us
     ag_us = timed_us(gather_only, args.steps, 3, ranks) if ranks.world > 1 else 0.0
+    push_us = timed_us(push_only, args.steps, 3, ranks) if push_only is not None else 0.0
+    workspace.check_status(ranks.dev)
     plan = info["plan"]
     idx_us = timed_us(lambda: indexer.kernel(*info["local_args"], plan.local_rows), args.steps, 3, ranks)
     qn, qp, ckv, kpe, scale = info["attention"]
     att_us = timed_us(lambda: sparse_attention.kernel(qn, qp, ckv, kpe, plan.all_rows, scale, info["out"], info["lse"]),
                       args.steps, 3, ranks)
-    us, ag_us, idx_us, att_us = ranks.max_over_ranks([us, ag_us, idx_us, att_us])
+    us, nccl_us, ag_us, push_us, idx_us, att_us = ranks.max_over_ranks([us, nccl_us, ag_us, push_us, idx_us, att_us])
+    if info["push_plan"] is not None:
+        info["push_plan"].close()
     if ranks.rank != 0:
         return None
     peak, _, kind = measured_peaks()
@@ -856,7 +892,15 @@ def run_cfg4(args, ranks):
     line = base_line(CFG4_METRIC, us, args, ranks, "strong", cfg4_config(ranks.world), clocks, 3)
     line["config"]["indexer"] = (f"request-sharded, {info['requests_on_rank0']} requests / "
                                  f"{info['cached_tokens_on_rank0']} cached tokens on rank 0")
-    line["stages"] = {"indexer_us": idx_us, "allgather_us": ag_us, "sparse_attention_us": att_us,
+    if ranks.world > 1:
+        line["config"]["collective"] = (
+            "index rows int32 [128,2048] (1 MiB) pushed into the peers' buffers by dsa_index_rows_exchange "
+            "(plain stores over NVLink, bounded wait); the NCCL all_gather of the same rows is timed beside it"
+            if push_step is not None else
+            f"all_gather int32 [128,2048] (1 MiB); peer push unavailable: {info['push_error']}")
+    line["stages"] = {"indexer_us": idx_us, "allgather_us": ag_us, "push_us": push_us,
+                      "layer_with_nccl_allgather_us": nccl_us, "layer_with_push_us": us if push_step is not None else None,
+                      "sparse_attention_us": att_us,
                       "attention_frac_of_peak": att_algo / (att_us * 1e-6) / 1e9 / peak}
     line["roofline"] = {"kernel": "sparse_attn_mma_kernel", "bound": "hbm",
                         "achieved": att_algo / (att_us * 1e-6) / 1e9, "peak": peak,

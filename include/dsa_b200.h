@@ -259,22 +259,24 @@ int dsa_peer_slab_destroy(void* ptr);
 
 /* Exchange of index rows between the GPUs of a head-sharded layer (no counterpart in the reference,
  * which is single-GPU: its operators meet only through the index tensor, indexer_baseline.py:82-90 ->
- * sparse_baseline.py:22-28).  Every rank owns one buffer `rows[rows_total][row_stride]` int32 and
- * one array `ready[rows_total]` uint32 (zero when created) that its peers can address;
- * `peer_rows[p]` / `peer_ready[p]` (HOST arrays of `world` device pointers, entry `rank` being the
- * caller's own) are those buffers as seen from this GPU.  The call copies the caller's local rows
- * [row_offset, row_offset + rows_local) -- already in its own buffer, `row_width` ids each -- into
- * the same rows of every peer's buffer with plain stores, then stores `epoch` into those rows' ready
- * words on every peer, then waits until every other row of its OWN ready array holds `epoch` or a
- * later value.  When the kernel has completed, rows_total rows are in the caller's own buffer.
- * `epoch` must grow by one per call on every rank (start at 1); two row buffers used alternately
- * (by the epoch's parity) keep a rank that runs ahead from overwriting rows a peer still reads.
- * The wait ends after `wait_limit_ns` (1 .. 1e10) with DSA_STATUS_WAIT_TIMEOUT in *status_dev; the
- * context stays usable.  One process per GPU; never run two ranks on one GPU. */
-int dsa_index_rows_exchange(int32_t* const* peer_rows, uint32_t* const* peer_ready, int world, int rank,
-                            int rows_local, int row_offset, int rows_total, int64_t row_stride,
-                            int row_width, uint32_t epoch, uint64_t wait_limit_ns,
-                            int32_t* status_dev, void* stream);
+ * sparse_baseline.py:22-28).  `rows` is the caller's own [rows_total][row_stride] int32 index tensor
+ * (ordinary device memory) whose rows [row_offset, row_offset + rows_local) the selection has just
+ * written.  Every rank also owns a staging buffer of rows_total x row_width 8-byte (id, epoch)
+ * pairs, zero when created, that its peers can address (dsa_peer_slab_create / _open);
+ * `peer_stage` is a HOST array of `world` device pointers to those buffers as seen from this GPU
+ * (entry `rank`: the caller's own).  One kernel stores the local rows as pairs into the same rows
+ * of every peer's staging buffer (plain 16-byte stores; nothing is read from a peer), and polls
+ * the other rows of its own staging buffer until every pair carries `epoch`, writing the ids into
+ * `rows`.  When it has completed, `rows` holds all rows_total rows.  `epoch` (never 0) must differ
+ * from the epoch of the call two steps earlier on every rank: count calls from 1.  Use two staging
+ * buffers alternately (by the epoch's parity): a rank can run one step ahead of a peer, not two.
+ * The poll ends after `wait_limit_ns` (1 .. 1e10) with DSA_STATUS_WAIT_TIMEOUT in *status_dev and
+ * the rows it could not complete left as they were; the context stays usable.  row_width and
+ * row_stride even, `rows` 8-byte aligned.  One process per GPU; never run two ranks on one GPU at
+ * the same time. */
+int dsa_index_rows_exchange(int32_t* rows, void* const* peer_stage, int world, int rank, int rows_local,
+                            int row_offset, int rows_total, int64_t row_stride, int row_width,
+                            uint32_t epoch, uint64_t wait_limit_ns, int32_t* status_dev, void* stream);
 
 /* Self-test of the bounded device-side waits (no counterpart in the reference, whose kernels spin
  * without a limit: sparse_fused.py:135-137).  One thread waits for at most `limit_ns` nanoseconds

@@ -123,9 +123,10 @@ def test_head_sharded_block_with_pushed_rows_on_two_gpus(tmp_path):
 
 def test_row_exchange_two_ranks_in_turn_on_one_gpu(cuda):
     """The exchange kernel with both ranks' buffers on one GPU, the ranks called one after the other
-    (never at the same time): rank 1 pushes and, with rank 0 silent, its wait runs out after the
-    2 ms it was given and reports DSA_STATUS_WAIT_TIMEOUT; rank 0 then pushes and finds rank 1's rows
-    already there.  Afterwards both buffers hold all rows."""
+    (never at the same time): rank 1 pushes and, with rank 0 silent, its poll runs out after the
+    2 ms it was given and reports DSA_STATUS_WAIT_TIMEOUT, leaving rank 0's rows as they were;
+    rank 0 then pushes and finds rank 1's rows already there; rank 1, called again, now finds
+    rank 0's.  A second epoch through the same staging buffers must not be satisfied by the first."""
     import ctypes
     for p in (ROOT, ROOT / "oracle"):
         if str(p) not in sys.path:
@@ -135,35 +136,41 @@ def test_row_exchange_two_ranks_in_turn_on_one_gpu(cuda):
     counts, width = [5, 3], 2048
     total = sum(counts)
     gen = torch.Generator(device=cuda).manual_seed(5)
-    truth = torch.randint(0, 1 << 20, (total, width), dtype=torch.int32, device=cuda, generator=gen)
-    rows = [torch.full((total, width), -7, dtype=torch.int32, device=cuda) for _ in range(2)]
-    ready = [torch.zeros(total, dtype=torch.int32, device=cuda) for _ in range(2)]
-    rows[0][:5] = truth[:5]
-    rows[1][5:] = truth[5:]
-    row_ptrs = (ctypes.c_void_p * 2)(rows[0].data_ptr(), rows[1].data_ptr())
-    ready_ptrs = (ctypes.c_void_p * 2)(ready[0].data_ptr(), ready[1].data_ptr())
     status = workspace.status_word(cuda)
+    stage = [torch.zeros(total, width, 2, dtype=torch.int32, device=cuda) for _ in range(2)]
+    stage_ptrs = (ctypes.c_void_p * 2)(stage[0].data_ptr(), stage[1].data_ptr())
+    rows = [torch.full((total, width), -7, dtype=torch.int32, device=cuda) for _ in range(2)]
 
-    def call(rank, limit_ns):
+    def call(rank, epoch, limit_ns=2_000_000):
         offset = sum(counts[:rank])
-        rc = lib.dsa_index_rows_exchange(ctypes.addressof(row_ptrs), ctypes.addressof(ready_ptrs), 2, rank,
-                                         counts[rank], offset, total, width, width, 1, limit_ns,
+        rc = lib.dsa_index_rows_exchange(rows[rank].data_ptr(), ctypes.addressof(stage_ptrs), 2, rank,
+                                         counts[rank], offset, total, width, width, epoch, limit_ns,
                                          status.data_ptr(), workspace.stream_handle(cuda))
         _lib.check(rc, "dsa_index_rows_exchange")
 
-    call(1, 2_000_000)
-    with pytest.raises(RuntimeError, match="0x1"):
-        workspace.check_status(cuda)
-    assert torch.equal(rows[0][5:], truth[5:]) and (ready[0][5:] == 1).all() and (ready[0][:5] == 0).all()
-    call(0, 2_000_000)
-    assert workspace.check_status(cuda) == 0
-    assert torch.equal(rows[0], truth) and torch.equal(rows[1], truth)
-    assert (ready[0] == 1).all() and (ready[1] == 1).all()
+    for epoch in (1, 2):
+        truth = torch.randint(-1, 1 << 20, (total, width), dtype=torch.int32, device=cuda, generator=gen)
+        before = rows[1][:5].clone()
+        rows[0][:5] = truth[:5]
+        rows[1][5:] = truth[5:]
+        call(1, epoch)
+        with pytest.raises(RuntimeError, match="0x1"):
+            workspace.check_status(cuda)
+        assert torch.equal(rows[1][:5], before)            # nothing taken: rank 0 has not sent this epoch
+        assert torch.equal(stage[0][5:, :, 0], truth[5:]) and (stage[0][5:, :, 1] == epoch).all()
+        call(0, epoch)
+        assert workspace.check_status(cuda) == 0
+        assert torch.equal(rows[0], truth)
+        call(1, epoch)
+        assert workspace.check_status(cuda) == 0
+        assert torch.equal(rows[1], truth)
     # argument checks
-    assert lib.dsa_index_rows_exchange(ctypes.addressof(row_ptrs), ctypes.addressof(ready_ptrs), 9, 0, 1, 0, 8,
-                                       width, width, 1, 1000, status.data_ptr(), None) < 0
-    assert lib.dsa_index_rows_exchange(ctypes.addressof(row_ptrs), ctypes.addressof(ready_ptrs), 2, 0, 5, 0, 8,
-                                       width, width, 1, 0, status.data_ptr(), None) < 0
+    bad = lib.dsa_index_rows_exchange(rows[0].data_ptr(), ctypes.addressof(stage_ptrs), 9, 0, 1, 0, 8, width, width,
+                                      1, 1000, status.data_ptr(), None)
+    assert bad < 0
+    bad = lib.dsa_index_rows_exchange(rows[0].data_ptr(), ctypes.addressof(stage_ptrs), 2, 0, 5, 0, 8, width, width,
+                                      0, 1000, status.data_ptr(), None)
+    assert bad < 0
 
 
 def test_head_sharded_block_on_two_gpus(tmp_path):
