@@ -171,6 +171,9 @@ class PeerPushPlan:
         self.total, self.width = sum(self.counts), width
         self.offset = sum(self.counts[:rank])
         self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("PeerPushPlan: the exchange kernel needs CUDA devices (use HeadShardedPlan "
+                               "for other process groups)")
         self.wait_limit_ns = int(wait_limit_ns)
         self.all_rows = torch.full((self.total, width), -1, dtype=torch.int32, device=self.device)
         self.local_rows = self.all_rows[self.offset: self.offset + self.counts[rank]]

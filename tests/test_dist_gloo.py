@@ -160,3 +160,12 @@ def test_head_sharded_plan_reuses_its_buffers(tmp_path):
     result = tmp_path / "result.txt"
     mp.spawn(_plan_worker, args=(2, _free_port(), str(result)), nprocs=2, join=True)
     assert result.read_text() == "ok"
+
+
+def test_peer_push_plan_refuses_cpu_ranks():
+    """The pushed exchange is a CUDA kernel over NVLink: on CPU ranks the plan says so instead of
+    falling back to anything (the all-gather plan is the one for other process groups)."""
+    import pytest
+    from auto_gpu_kernel_b200 import dist as dsa_dist
+    with pytest.raises(RuntimeError, match="CUDA"):
+        dsa_dist.PeerPushPlan([2, 2], 0, "cpu")
