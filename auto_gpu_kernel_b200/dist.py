@@ -110,30 +110,50 @@ class _PeerSlabs:
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         own, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
         with self._guard(self.device):
-            _lib.check(lib.dsa_peer_slab_create(nbytes, ctypes.addressof(own), ctypes.addressof(handle)),
-                       "dsa_peer_slab_create")
-        self.own, self.nbytes = own.value, nbytes
+            rc = lib.dsa_peer_slab_create(nbytes, ctypes.addressof(own), ctypes.addressof(handle))
+        error = None if rc == 0 else f"dsa_peer_slab_create returned {rc}"
+        self.own, self.nbytes = (own.value if rc == 0 else None), nbytes
         handles = [None] * world
-        dist.all_gather_object(handles, handle.raw, group=group)
+        dist.all_gather_object(handles, handle.raw if rc == 0 else None, group=group)
         self.ptrs, self._opened = [], []
         for r, raw in enumerate(handles):
+            if error is not None:
+                break
+            if raw is None:
+                error = f"rank {r} has no buffer"
+                break
             if r == rank:
                 self.ptrs.append(self.own)
                 continue
             buf, got = ctypes.create_string_buffer(raw, 64), ctypes.c_void_p()
             with self._guard(self.device):
-                _lib.check(lib.dsa_peer_slab_open(ctypes.addressof(buf), ctypes.addressof(got)),
-                           "dsa_peer_slab_open")
+                rc = lib.dsa_peer_slab_open(ctypes.addressof(buf), ctypes.addressof(got))
+            if rc != 0:
+                error = f"dsa_peer_slab_open(rank {r}) returned {rc}"
+                break
             self.ptrs.append(got.value)
             self._opened.append(got.value)
+        self._group = group
+        # every slab is mapped everywhere before anyone writes -- or nobody goes on: the outcome is
+        # agreed on by all ranks, so a failure on one of them cannot leave the others waiting
+        outcomes = [None] * world
+        dist.all_gather_object(outcomes, error, group=group)
+        failed = [f"rank {r}: {e}" for r, e in enumerate(outcomes) if e is not None]
+        if failed:
+            self.tensor = None
+            self._release(barrier=False)    # nothing was written through the mappings yet
+            raise RuntimeError("peer buffers could not be mapped (" + "; ".join(failed) + ")")
         with self._guard(self.device):
             self.tensor = torch.as_tensor(_DeviceBytes(self.own, nbytes), device=self.device)
-        self._group = group
-        dist.barrier(group=group)      # every slab is mapped everywhere before anyone writes
 
     def close(self):
-        """Unmap the peers' slabs, then (after a barrier) free the own one."""
-        if self.own is None:
+        """Unmap the peers' slabs, then (after a barrier) free the own one.  Collective."""
+        self._release(barrier=True)
+
+    def _release(self, barrier: bool):
+        if self.own is None and not self._opened:
+            if barrier and dist.is_initialized():
+                dist.barrier(group=self._group)
             return
         lib = self._lib.load()
         self.tensor = None
@@ -142,9 +162,10 @@ class _PeerSlabs:
             for p in self._opened:
                 lib.dsa_peer_slab_close(p)
             self._opened = []
-            if dist.is_initialized():
+            if barrier and dist.is_initialized():
                 dist.barrier(group=self._group)
-            lib.dsa_peer_slab_destroy(self.own)
+            if self.own is not None:
+                lib.dsa_peer_slab_destroy(self.own)
         self.own = None
 
 
@@ -194,6 +215,13 @@ class PeerPushPlan:
         """Release the shared buffers (collective: every rank calls it)."""
         if self._slabs is not None:
             self._slabs.close()
+            self._slabs = None
+
+    def abandon(self):
+        """Release this rank's side without meeting the others (for a set-up that another rank could
+        not complete: nothing has been exchanged yet)."""
+        if self._slabs is not None:
+            self._slabs._release(barrier=False)
             self._slabs = None
 
     def gather(self):

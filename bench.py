@@ -406,6 +406,13 @@ def head_sharded_setup(ranks, batch=128, lo=16384, hi=65536):
             push_plan = dsa_dist.PeerPushPlan(counts, rank, dev)
         except Exception as exc:   # noqa: BLE001 - reported in the JSON line
             push_error = f"{type(exc).__name__}: {exc}"[:200]
+        # all ranks or none (PeerPushPlan agrees on its own outcome; this covers anything else)
+        every = [None] * world
+        torch.distributed.all_gather_object(every, push_error)
+        if any(e is not None for e in every) and push_plan is not None:
+            push_plan.abandon()
+            push_plan = None
+        push_error = next((e for e in every if e is not None), None)
     my_tokens = sum(lens[i] for i in mine)
     return make_step(plan), gather_only, {"requests_on_rank0": len(mine), "cached_tokens_on_rank0": my_tokens,
                                           "lens": lens, "local_args": local_args,
@@ -643,9 +650,13 @@ def run_headline(args, ranks):
         hs_step, gather_only, info = head_sharded_setup(ranks)
         hs_us = timed_us(hs_step, args.steps, args.warmup, ranks)
         ag_us = timed_us(gather_only, args.steps, args.warmup, ranks)
+        workspace.check_status(dev)
         hsp_us = timed_us(info["push_step"], args.steps, args.warmup, ranks) if info["push_step"] else 0.0
         push_us = timed_us(info["push_only"], args.steps, args.warmup, ranks) if info["push_only"] else 0.0
-        workspace.check_status(dev)
+        try:
+            workspace.check_status(dev)
+        except RuntimeError:      # a poll ran out on this rank: the pushed layer is reported as not measured
+            hsp_us = push_us = float("inf")
         if info["push_plan"] is not None:
             info["push_plan"].close()
         del hs_step, gather_only, info
@@ -657,6 +668,7 @@ def run_headline(args, ranks):
         workspace.check_status(dev)
 
     vals = ranks.max_over_ranks([step_us, e2e, idx_us, att_us, score_us, idx_sep_us, att_sep_us] + extra_vals)
+    vals = [0.0 if v == float("inf") else v for v in vals]
     step_us, e2e, idx_us, att_us, score_us, idx_sep_us, att_sep_us = vals[:7]
     if ranks.rank != 0:
         return None
