@@ -49,7 +49,10 @@ SIGNATURES = {
     "dsa_peer_slab_close": (_c_int, [_ptr]),
     "dsa_peer_slab_destroy": (_c_int, [_ptr]),
     "dsa_index_rows_exchange": (_c_int, [_ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_i64,
-                                         _c_int, ctypes.c_uint32, ctypes.c_uint64, _ptr, _ptr]),
+                                         _c_int, ctypes.c_uint32, _c_int, ctypes.c_uint64, _ptr, _ptr]),
+    "dsa_indexer_topk_send": (_c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _ptr, _c_i64, _c_int, _c_int,
+                                       _c_int, _ptr, _c_size, _ptr, _c_int, _c_int, _c_int,
+                                       ctypes.c_uint32, _ptr, _ptr]),
     "dsa_selftest_wait_expiry": (_c_int, [ctypes.c_uint64, _ptr, _ptr, _ptr]),
     "dsa_selftest_mma_rate": (_c_int, [_c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr]),
 }

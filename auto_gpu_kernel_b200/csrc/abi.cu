@@ -14,7 +14,8 @@ cudaError_t launch_indexer_score_tc(const void*, const void*, const float*, cons
                                     const int32_t*, int64_t, float*, int64_t, int, int, int, int,
                                     uint32_t*, uint32_t*, int32_t*, cudaStream_t);
 cudaError_t launch_topk_select_hist(const float*, int64_t, const int32_t*, const int32_t*, int64_t,
-                                    int32_t*, int64_t, int, int, uint32_t*, int32_t*, cudaStream_t);
+                                    int32_t*, int64_t, int, int, uint32_t*, const RowSend*, int32_t*,
+                                    cudaStream_t);
 bool topk_select_hist_supports(int batch, int max_pages);
 cudaError_t launch_topk_select(const float*, int64_t, const int32_t*, const int32_t*, int64_t,
                                int32_t*, int64_t, int, int, uint32_t*, int32_t*, cudaStream_t);
@@ -25,8 +26,8 @@ cudaError_t launch_sparse_attn_tc(const void*, const void*, const void*, const v
                                   const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
                                   void*, int32_t*, cudaStream_t);
 size_t at_tc_workspace_bytes_auto(int tokens, int topk);
-cudaError_t launch_index_rows_exchange(int32_t*, uint2* const*, int, int, int, int, int, int64_t, int,
-                                       uint32_t, uint64_t, int32_t*, cudaStream_t);
+cudaError_t launch_index_rows_exchange(int32_t*, const RowSend&, int, int, int64_t, int, uint64_t, int32_t*,
+                                       cudaStream_t);
 cudaError_t launch_sparse_attn_mma(const void*, const void*, const void*, const void*,
                                    const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
                                    void*, int32_t*, cudaStream_t);
@@ -152,11 +153,14 @@ int dsa_topk_select(const float* scores, int64_t score_stride, const int32_t* se
                                                   static_cast<cudaStream_t>(stream)));
 }
 
-int dsa_indexer_topk(const void* q_fp8, const void* k_cache, const float* weights,
-                     const int32_t* seq_lens, const int32_t* block_table,
-                     int64_t block_table_stride, int32_t* topk_out, int64_t topk_stride, int batch,
-                     int num_pages, int max_pages, void* workspace, size_t workspace_bytes,
-                     int32_t* status_dev, void* stream) {
+// `send` (may be null): where finished rows go in a head-sharded layer.  *sent tells whether the
+// selection kernel has sent them itself (the histogram path) or the caller still has to.
+static int indexer_topk_impl(const void* q_fp8, const void* k_cache, const float* weights,
+                             const int32_t* seq_lens, const int32_t* block_table,
+                             int64_t block_table_stride, int32_t* topk_out, int64_t topk_stride, int batch,
+                             int num_pages, int max_pages, void* workspace, size_t workspace_bytes,
+                             int32_t* status_dev, void* stream, const dsa::RowSend* send, bool* sent) {
+  if (sent) *sent = false;
   if (batch == 0) return DSA_OK;
   if (!workspace) return DSA_ERR_NULL_POINTER;
   if (workspace_bytes < dsa_indexer_workspace_bytes(batch, max_pages))
@@ -182,9 +186,10 @@ int dsa_indexer_topk(const void* q_fp8, const void* k_cache, const float* weight
     int rc = scores_impl(q_fp8, k_cache, weights, seq_lens, block_table, block_table_stride, scores,
                          stride, batch, num_pages, max_pages, 0, 1, nullptr, ghist, status_dev, stream);
     if (rc != DSA_OK) return rc;
+    if (sent) *sent = send != nullptr;
     return static_cast<int>(dsa::launch_topk_select_hist(
         scores, stride, seq_lens, block_table, block_table_stride, topk_out, topk_stride, batch,
-        max_pages, ghist, status_dev, static_cast<cudaStream_t>(stream)));
+        max_pages, ghist, send, status_dev, static_cast<cudaStream_t>(stream)));
   }
   if (long_rows) {
     int rc = scores_impl(q_fp8, k_cache, weights, seq_lens, block_table, block_table_stride, scores,
@@ -199,6 +204,57 @@ int dsa_indexer_topk(const void* q_fp8, const void* k_cache, const float* weight
                                                   block_table_stride, topk_out, topk_stride, batch,
                                                   max_pages, minmax, status_dev,
                                                   static_cast<cudaStream_t>(stream)));
+}
+
+int dsa_indexer_topk(const void* q_fp8, const void* k_cache, const float* weights,
+                     const int32_t* seq_lens, const int32_t* block_table,
+                     int64_t block_table_stride, int32_t* topk_out, int64_t topk_stride, int batch,
+                     int num_pages, int max_pages, void* workspace, size_t workspace_bytes,
+                     int32_t* status_dev, void* stream) {
+  return indexer_topk_impl(q_fp8, k_cache, weights, seq_lens, block_table, block_table_stride, topk_out,
+                           topk_stride, batch, num_pages, max_pages, workspace, workspace_bytes,
+                           status_dev, stream, nullptr, nullptr);
+}
+
+static int fill_row_send(dsa::RowSend* xs, void* const* peer_stage, int world, int rank, int row_offset,
+                         int row_width, uint32_t epoch) {
+  if (!peer_stage) return DSA_ERR_NULL_POINTER;
+  if (world < 1 || world > dsa::kRowSendMaxWorld || rank < 0 || rank >= world || row_offset < 0 ||
+      row_width <= 0 || row_width % 2 != 0 || epoch == 0)
+    return DSA_ERR_BAD_SHAPE;
+  *xs = dsa::RowSend{};
+  for (int p = 0; p < world; ++p) {
+    if (!peer_stage[p]) return DSA_ERR_NULL_POINTER;
+    if (!aligned16(peer_stage[p])) return DSA_ERR_MISALIGNED;
+    xs->stage[p] = static_cast<uint2*>(peer_stage[p]);
+  }
+  xs->world = world;
+  xs->rank = rank;
+  xs->row_offset = row_offset;
+  xs->row_width = row_width;
+  xs->epoch = epoch;
+  return DSA_OK;
+}
+
+int dsa_indexer_topk_send(const void* q_fp8, const void* k_cache, const float* weights,
+                          const int32_t* seq_lens, const int32_t* block_table,
+                          int64_t block_table_stride, int32_t* topk_out, int64_t topk_stride, int batch,
+                          int num_pages, int max_pages, void* workspace, size_t workspace_bytes,
+                          void* const* peer_stage, int world, int rank, int row_offset, uint32_t epoch,
+                          int32_t* status_dev, void* stream) {
+  dsa::RowSend xs;
+  int rc = fill_row_send(&xs, peer_stage, world, rank, row_offset, dsa::kTopK, epoch);
+  if (rc != DSA_OK) return rc;
+  if (topk_stride % 2 != 0 || (reinterpret_cast<uintptr_t>(topk_out) & 7u)) return DSA_ERR_MISALIGNED;
+  bool sent = false;
+  rc = indexer_topk_impl(q_fp8, k_cache, weights, seq_lens, block_table, block_table_stride, topk_out,
+                         topk_stride, batch, num_pages, max_pages, workspace, workspace_bytes, status_dev,
+                         stream, &xs, &sent);
+  if (rc != DSA_OK || sent || batch == 0 || world == 1) return rc;
+  // the other selection kernels do not send: a push-only pass over the finished rows
+  int32_t* base = topk_out - (int64_t)row_offset * topk_stride;   // row i of the exchange = base + i * stride
+  return static_cast<int>(dsa::launch_index_rows_exchange(base, xs, batch, row_offset + batch, topk_stride, 1,
+                                                          1, status_dev, static_cast<cudaStream_t>(stream)));
 }
 
 size_t dsa_sparse_attn_workspace_bytes(int tokens, int heads, int topk) {
@@ -302,24 +358,21 @@ int dsa_peer_slab_destroy(void* ptr) { return ptr ? static_cast<int>(cudaFree(pt
 
 int dsa_index_rows_exchange(int32_t* rows, void* const* peer_stage, int world, int rank, int rows_local,
                             int row_offset, int rows_total, int64_t row_stride, int row_width,
-                            uint32_t epoch, uint64_t wait_limit_ns, int32_t* status_dev, void* stream) {
-  if (!rows || !peer_stage) return DSA_ERR_NULL_POINTER;
-  if (world < 1 || world > 8 || rank < 0 || rank >= world || rows_local < 0 || row_offset < 0 ||
-      rows_total < row_offset + rows_local || row_width <= 0 || row_width % 2 != 0 ||
-      row_stride < row_width || row_stride % 2 != 0 || epoch == 0 || wait_limit_ns == 0 ||
+                            uint32_t epoch, int mode, uint64_t wait_limit_ns, int32_t* status_dev,
+                            void* stream) {
+  if (!rows) return DSA_ERR_NULL_POINTER;
+  dsa::RowSend xs;
+  int rc = fill_row_send(&xs, peer_stage, world, rank, row_offset, row_width, epoch);
+  if (rc != DSA_OK) return rc;
+  if (rows_local < 0 || rows_total < row_offset + rows_local || row_stride < row_width ||
+      row_stride % 2 != 0 || mode < 1 || mode > 3 || wait_limit_ns == 0 ||
       wait_limit_ns > 10000000000ull)
     return DSA_ERR_BAD_SHAPE;
   if (reinterpret_cast<uintptr_t>(rows) & 7u) return DSA_ERR_MISALIGNED;
-  uint2* stage[8] = {};
-  for (int p = 0; p < world; ++p) {
-    if (!peer_stage[p]) return DSA_ERR_NULL_POINTER;
-    if (!aligned16(peer_stage[p])) return DSA_ERR_MISALIGNED;
-    stage[p] = static_cast<uint2*>(peer_stage[p]);
-  }
   if (rows_total == 0) return DSA_OK;
-  return static_cast<int>(dsa::launch_index_rows_exchange(
-      rows, stage, world, rank, rows_local, row_offset, rows_total, row_stride, row_width, epoch,
-      wait_limit_ns, status_dev, static_cast<cudaStream_t>(stream)));
+  return static_cast<int>(dsa::launch_index_rows_exchange(rows, xs, rows_local, rows_total, row_stride,
+                                                          mode, wait_limit_ns, status_dev,
+                                                          static_cast<cudaStream_t>(stream)));
 }
 
 int dsa_index_cache_write(const void* keys, int key_dtype, int64_t key_stride, const int32_t* slots,

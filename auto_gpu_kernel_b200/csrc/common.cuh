@@ -61,6 +61,38 @@ constexpr int kHistMaxBatch = 1024;       // larger batches take the min/max pat
 constexpr int kHistBins = 4096;
 constexpr size_t kHistRegionBytes = (size_t)kHistMaxBatch * kHistBins * sizeof(uint32_t);
 
+// Where the selection sends a finished index row in a head-sharded layer: every rank's staging
+// buffer of (id, epoch) pairs as seen from this GPU (entry `rank` unused).  world <= 1: nothing is sent.
+constexpr int kRowSendMaxWorld = 8;
+struct RowSend {
+  uint2* stage[kRowSendMaxWorld];
+  int world, rank, row_offset, row_width;
+  uint32_t epoch;
+};
+// Store row `index` (row_width ids at `row`, complete and visible to this CTA) into every peer's
+// staging buffer as (id, epoch) pairs, 16 bytes per store; by all threads of the calling CTA.
+__device__ __forceinline__ void send_row_pairs(const RowSend& xs, const int32_t* row, int index) {
+  const int units = xs.row_width / 2;
+  for (int u = threadIdx.x; u < units; u += blockDim.x) {
+    const int2 v = __ldcg(reinterpret_cast<const int2*>(row) + u);
+    const uint4 packed = make_uint4((uint32_t)v.x, xs.epoch, (uint32_t)v.y, xs.epoch);
+    // (constant indices: the table stays in the kernel's parameter space, no local copy)
+#pragma unroll
+    for (int p = 0; p < kRowSendMaxWorld; ++p) {
+      if (p < xs.world && p != xs.rank)
+        reinterpret_cast<uint4*>(xs.stage[p] + (size_t)index * xs.row_width)[u] = packed;
+    }
+  }
+}
+// This rank's own staging buffer.
+__device__ __forceinline__ uint2* own_stage(const RowSend& xs) {
+  uint2* p = xs.stage[0];
+#pragma unroll
+  for (int r = 1; r < kRowSendMaxWorld; ++r)
+    if (r == xs.rank) p = xs.stage[r];
+  return p;
+}
+
 // -inf and NaN scores are ranked as this value by the selection (and by the scorer's min / max).
 constexpr float kScoreFloor = -3.0e38f;
 

@@ -12,6 +12,9 @@
 //     carries this call's epoch, and writes the ids into the rank's index tensor.
 // A pair that carries the epoch is its own proof of arrival, so the latency is one NVLink trip
 // instead of data + fence + flag.  The poll has a time limit that ends in DSA_STATUS_WAIT_TIMEOUT.
+// The push half can also run at the end of the selection kernel (topk_select_hist_kernel sends
+// every row as soon as it is complete, while other requests are still being selected); this kernel
+// is then launched for the take half only (`mode`: 1 = push, 2 = take, 3 = both).
 // Nothing is ever read from a peer's memory, and nothing on this GPU waits for another kernel of
 // this GPU.  The host alternates two staging buffers with the epoch's parity: a rank can run at
 // most one step ahead of a peer's take, so it never overwrites pairs that are still being read.
@@ -22,11 +25,6 @@
 namespace dsa {
 
 constexpr int kXchThreads = 256;
-constexpr int kXchMaxWorld = 8;
-
-struct XchPeers {
-  uint2* stage[kXchMaxWorld];   // every rank's [rows_total][row_width] (id, epoch) staging buffer
-};
 
 namespace {
 
@@ -38,34 +36,28 @@ __device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
 }
 
 __global__ void __launch_bounds__(kXchThreads)
-index_rows_exchange_kernel(int32_t* __restrict__ rows, XchPeers peers, int world, int rank,
-                           int rows_local, int row_offset, int rows_total, int64_t row_stride,
-                           int row_width, uint32_t epoch, uint64_t limit_ns, int32_t* status) {
+index_rows_exchange_kernel(int32_t* __restrict__ rows, const __grid_constant__ RowSend xs, int rows_local, int rows_total,
+                           int64_t row_stride, int mode, uint64_t limit_ns, int32_t* status) {
+  const int rank = xs.rank, row_offset = xs.row_offset, row_width = xs.row_width;
+  const uint32_t epoch = xs.epoch;
   const int tid = threadIdx.x;
   // the local rows come from the selection kernel before us in the stream
   ptx::grid_dependency_wait();
   ptx::launch_dependents();   // the attention behind us waits for this whole kernel by itself
   const int pairs2 = row_width / 2;   // 16-byte units (two pairs) per row
   // ---- push: local row b by CTA b, b + grid, ... (before any take: a CTA never polls while it
-  //      still has rows to send) ----
-  for (int b = blockIdx.x; b < rows_local; b += gridDim.x) {
-    const int i = row_offset + b;
-    const int32_t* row = rows + (size_t)i * row_stride;
-    for (int u = tid; u < pairs2; u += kXchThreads) {
-      const int2 v = __ldcg(reinterpret_cast<const int2*>(row) + u);
-      const uint4 packed = make_uint4((uint32_t)v.x, epoch, (uint32_t)v.y, epoch);
-      for (int p = 0; p < world; ++p) {
-        if (p == rank) continue;
-        reinterpret_cast<uint4*>(peers.stage[p] + (size_t)i * row_width)[u] = packed;
-      }
-    }
+  //      still has rows to send); skipped when the selection kernel has sent them itself ----
+  if (mode & 1) {
+    for (int b = blockIdx.x; b < rows_local; b += gridDim.x)
+      send_row_pairs(xs, rows + (size_t)(row_offset + b) * row_stride, row_offset + b);
   }
+  if (!(mode & 2)) return;
   // ---- take: the k-th remote row by CTA k, k + grid, ... ----
   const int rows_remote = rows_total - rows_local;
   for (int k = blockIdx.x; k < rows_remote; k += gridDim.x) {
     const int i = k < row_offset ? k : k + rows_local;
     int32_t* row = rows + (size_t)i * row_stride;
-    const uint4* src = reinterpret_cast<const uint4*>(peers.stage[rank] + (size_t)i * row_width);
+    const uint4* src = reinterpret_cast<const uint4*>(own_stage(xs) + (size_t)i * row_width);
     uint64_t t0 = 0;
     bool gave_up = false;
     for (int u = tid; u < pairs2; u += kXchThreads) {
@@ -87,14 +79,12 @@ index_rows_exchange_kernel(int32_t* __restrict__ rows, XchPeers peers, int world
 
 }  // namespace
 
-cudaError_t launch_index_rows_exchange(int32_t* rows, uint2* const* peer_stage, int world, int rank,
-                                       int rows_local, int row_offset, int rows_total, int64_t row_stride,
-                                       int row_width, uint32_t epoch, uint64_t limit_ns, int32_t* status,
+cudaError_t launch_index_rows_exchange(int32_t* rows, const RowSend& xs, int rows_local, int rows_total,
+                                       int64_t row_stride, int mode, uint64_t limit_ns, int32_t* status,
                                        cudaStream_t stream) {
-  XchPeers peers = {};
-  for (int p = 0; p < world; ++p) peers.stage[p] = peer_stage[p];
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)min(max(rows_total, 1), 1024));
+  const int ctas = (mode & 2) ? rows_total : rows_local;
+  cfg.gridDim = dim3((unsigned)min(max(ctas, 1), 1024));
   cfg.blockDim = dim3(kXchThreads);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -102,8 +92,8 @@ cudaError_t launch_index_rows_exchange(int32_t* rows, uint2* const* peer_stage, 
   attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled();
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, index_rows_exchange_kernel, rows, peers, world, rank, rows_local,
-                            row_offset, rows_total, row_stride, row_width, epoch, limit_ns, status);
+  return cudaLaunchKernelEx(&cfg, index_rows_exchange_kernel, rows, xs, rows_local, rows_total,
+                            row_stride, mode, limit_ns, status);
 }
 
 }  // namespace dsa

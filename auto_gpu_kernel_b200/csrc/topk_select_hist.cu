@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(kShThreads, 1)
 topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
                         const int32_t* __restrict__ seq_lens, const int32_t* __restrict__ block_table,
                         int64_t bt_stride, int32_t* __restrict__ out, int64_t out_stride,
-                        int max_pages, uint32_t* __restrict__ ghist, int32_t* status) {
+                        int max_pages, uint32_t* __restrict__ ghist, const __grid_constant__ RowSend xs, int32_t* status) {
   extern __shared__ float row_s[];
   __shared__ ShShared sh;
   cg::cluster_group cluster = cg::this_cluster();
@@ -142,10 +142,22 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
   ptx::launch_dependents();
   ptx::grid_dependency_wait();
 
+  // Head-sharded layers: the first CTA sends the finished row to the peers' staging buffers, while
+  // other requests are still being selected (the take side is index_rows_exchange_kernel).
+  auto send_row = [&]() {
+    if (xs.world > 1) {
+      __syncthreads();
+      send_row_pairs(xs, out_row, xs.row_offset + b);
+    }
+  };
   if (len <= kTopK) {  // every token is selected: no scores, no histogram (uniform over the cluster)
     __syncthreads();
     for (int i = crank * kShThreads + tid; i < kTopK; i += csize * kShThreads)
       out_row[i] = i < len ? slot_of(i) : -1;
+    if (xs.world > 1) {
+      if (csize > 1) cluster.sync();   // the other CTAs' part of the row
+      if (crank == 0) send_row();
+    }
     return;
   }
 
@@ -191,6 +203,7 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
   const uint32_t edge = sh.edge, above = sh.above, in_edge = sh.in_edge;
   if (in_edge == 0xFFFFFFFFu) {   // the histogram does not hold this row (workspace not zeroed?)
     if (tid == 0 && crank == 0) raise_status(status, DSA_STATUS_TOPK_COUNT);
+    if (crank == 0) send_row();   // flagged; the peers still get a row, so that none of them waits
     return;                       // uniform over the cluster: every CTA read the same histogram
   }
   // A cluster of one or two meets only once more (after the writing pass).  Its first CTA's digit
@@ -323,6 +336,7 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
     // the histogram is not this row's (junk in the workspace): the places above were not the
     // elements' own, and candidate entries may be missing -- flag the call and leave the row
     if (tid == 0) raise_status(status, DSA_STATUS_TOPK_COUNT);
+    send_row();
     return;
   }
 
@@ -442,6 +456,7 @@ topk_select_hist_kernel(const float* __restrict__ scores, int64_t score_stride,
   }
   __syncthreads();
   if (tid == 0 && sh.emit_cnt != need) raise_status(status, DSA_STATUS_TOPK_COUNT);
+  send_row();
 }
 
 // CTAs per request: as many as fit in one wave, more when a CTA's share of the longest possible
@@ -464,7 +479,7 @@ bool topk_select_hist_supports(int batch, int max_pages) {
 cudaError_t launch_topk_select_hist(const float* scores, int64_t score_stride, const int32_t* seq_lens,
                                     const int32_t* block_table, int64_t bt_stride, int32_t* out,
                                     int64_t out_stride, int batch, int max_pages, uint32_t* ghist,
-                                    int32_t* status, cudaStream_t stream) {
+                                    const RowSend* send, int32_t* status, cudaStream_t stream) {
   static std::atomic<uint64_t> smem_opted{0};
   {
     cudaError_t e = opt_in_dynamic_smem(reinterpret_cast<const void*>(topk_select_hist_kernel),
@@ -487,8 +502,10 @@ cudaError_t launch_topk_select_hist(const float* scores, int64_t score_stride, c
   attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled();
   cfg.attrs = attr;
   cfg.numAttrs = 2;
+  RowSend xs = {};
+  if (send != nullptr) xs = *send;
   return cudaLaunchKernelEx(&cfg, topk_select_hist_kernel, scores, score_stride, seq_lens,
-                            block_table, bt_stride, out, out_stride, max_pages, ghist, status);
+                            block_table, bt_stride, out, out_stride, max_pages, ghist, xs, status);
 }
 
 }  // namespace dsa

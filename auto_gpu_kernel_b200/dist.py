@@ -210,6 +210,7 @@ class PeerPushPlan:
         self._ctypes = ctypes
         self._lib, self._workspace = _lib, workspace
         self.epoch = 0
+        self._sent = 0
 
     def close(self):
         """Release the shared buffers (collective: every rank calls it)."""
@@ -224,14 +225,33 @@ class PeerPushPlan:
             self._slabs._release(barrier=False)
             self._slabs = None
 
+    def _epoch_word(self, epoch):
+        return ((epoch - 1) % 0xFFFFFFFF) + 1     # never 0
+
+    def run_indexer(self, q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table):
+        """The rank's indexer with the sends fused into its selection kernel: writes `local_rows`
+        and stores every finished row into the peers' staging buffers of the step that the next
+        `gather()` completes (which then only takes)."""
+        from . import indexer
+        nxt = self.epoch + 1
+        send = None
+        if self.world > 1 and q_index_fp8.shape[0] > 0 and block_table.shape[1] > 0:
+            send = (self._ctypes.addressof(self._stage_ptrs[nxt & 1]), self.world, self.rank, self.offset,
+                    self._epoch_word(nxt))
+        indexer.kernel(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table, self.local_rows,
+                       send=send)
+        if send is not None:
+            self._sent = nxt
+
     def gather(self):
         self.epoch += 1
+        mode = 2 if self._sent == self.epoch else 3
         lib = self._lib.load()
         with self._workspace.device_guard(self.device):
             rc = lib.dsa_index_rows_exchange(
                 self.all_rows.data_ptr(), self._ctypes.addressof(self._stage_ptrs[self.epoch & 1]),
                 self.world, self.rank, self.counts[self.rank], self.offset, self.total,
-                self.all_rows.stride(0), self.width, ((self.epoch - 1) % 0xFFFFFFFF) + 1,
+                self.all_rows.stride(0), self.width, self._epoch_word(self.epoch), mode,
                 self.wait_limit_ns, self._workspace.status_word(self.device).data_ptr(),
                 self._workspace.stream_handle(self.device))
         self._lib.check(rc, "dsa_index_rows_exchange")
@@ -266,12 +286,18 @@ def decode_block_head_sharded(idx_args_local, counts, q_nope_heads, q_pe_heads, 
                      of the rank's own rows)
     Returns the gathered [B, 2048] index tensor.
     """
-    if indexer_fn is None or attention_fn is None:
-        indexer_fn, attention_fn = _default_ops()
     rank = dist.get_rank(group) if dist.is_initialized() else 0
+    fused = indexer_fn is None and hasattr(plan, "run_indexer")
+    if indexer_fn is None or attention_fn is None:
+        default_indexer, default_attention = _default_ops()
+        indexer_fn = indexer_fn or default_indexer
+        attention_fn = attention_fn or default_attention
     if plan is None:
         plan = HeadShardedPlan(counts, rank, q_nope_heads.device, group)
-    indexer_fn(*idx_args_local, plan.local_rows)
+    if fused:
+        plan.run_indexer(*idx_args_local)      # the selection kernel sends the rows itself
+    else:
+        indexer_fn(*idx_args_local, plan.local_rows)
     all_indices = plan.gather()
     if local_indices is not None:
         local_indices.copy_(plan.local_rows)

@@ -43,9 +43,13 @@ def _check(q, cache, weights, seq_lens, block_table):
         raise ValueError("block_table rows must be dense (stride(1) == 1)")
 
 
-def kernel(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table, topk_indices):
+def kernel(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table, topk_indices, send=None):
     """Write the top-2048 global slot ids of every request into `topk_indices` ([B,2048] int32,
-    -1 padded).  Enqueued on the current stream; returns None without synchronising."""
+    -1 padded).  Enqueued on the current stream; returns None without synchronising.
+
+    `send` (head-sharded layers only, see `dist.PeerPushPlan`): (address of the host array of the
+    peers' staging buffers, world, rank, row_offset, epoch) -- every finished row is then also
+    stored into the peers' memory (`dsa_indexer_topk_send`)."""
     _check(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table)
     batch = q_index_fp8.shape[0]
     if topk_indices.shape != (batch, TOPK) or topk_indices.dtype != torch.int32 \
@@ -63,13 +67,22 @@ def kernel(q_index_fp8, k_index_cache_fp8, weights, seq_lens, block_table, topk_
     ws = workspace.get(dev, "indexer", need)
     status = workspace.status_word(dev)
     with workspace.device_guard(dev):
-        rc = lib.dsa_indexer_topk(
-            q_index_fp8.data_ptr(), k_index_cache_fp8.data_ptr(), weights.data_ptr(),
-            seq_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0),
-            topk_indices.data_ptr(), topk_indices.stride(0), batch, k_index_cache_fp8.shape[0],
-            max_pages, ws.data_ptr(), ws.numel(), status.data_ptr(),
-            workspace.stream_handle(dev))
-    _lib.check(rc, "dsa_indexer_topk")
+        if send is None:
+            rc = lib.dsa_indexer_topk(
+                q_index_fp8.data_ptr(), k_index_cache_fp8.data_ptr(), weights.data_ptr(),
+                seq_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0),
+                topk_indices.data_ptr(), topk_indices.stride(0), batch, k_index_cache_fp8.shape[0],
+                max_pages, ws.data_ptr(), ws.numel(), status.data_ptr(),
+                workspace.stream_handle(dev))
+        else:
+            stage_array, world, rank, row_offset, epoch = send
+            rc = lib.dsa_indexer_topk_send(
+                q_index_fp8.data_ptr(), k_index_cache_fp8.data_ptr(), weights.data_ptr(),
+                seq_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0),
+                topk_indices.data_ptr(), topk_indices.stride(0), batch, k_index_cache_fp8.shape[0],
+                max_pages, ws.data_ptr(), ws.numel(), stage_array, world, rank, row_offset, epoch,
+                status.data_ptr(), workspace.stream_handle(dev))
+    _lib.check(rc, "dsa_indexer_topk" if send is None else "dsa_indexer_topk_send")
     return None
 
 

@@ -271,12 +271,30 @@ int dsa_peer_slab_destroy(void* ptr);
  * from the epoch of the call two steps earlier on every rank: count calls from 1.  Use two staging
  * buffers alternately (by the epoch's parity): a rank can run one step ahead of a peer, not two.
  * The poll ends after `wait_limit_ns` (1 .. 1e10) with DSA_STATUS_WAIT_TIMEOUT in *status_dev and
- * the rows it could not complete left as they were; the context stays usable.  row_width and
- * row_stride even, `rows` 8-byte aligned.  One process per GPU; never run two ranks on one GPU at
- * the same time. */
+ * the rows it could not complete left as they were; the context stays usable.  `mode`: 1 = only
+ * store the local rows (push), 2 = only take the peers' rows (after dsa_indexer_topk_send, which has
+ * sent the local ones), 3 = both.  row_width and row_stride even, `rows` 8-byte aligned.  One
+ * process per GPU; never run two ranks on one GPU at the same time. */
 int dsa_index_rows_exchange(int32_t* rows, void* const* peer_stage, int world, int rank, int rows_local,
                             int row_offset, int rows_total, int64_t row_stride, int row_width,
-                            uint32_t epoch, uint64_t wait_limit_ns, int32_t* status_dev, void* stream);
+                            uint32_t epoch, int mode, uint64_t wait_limit_ns, int32_t* status_dev,
+                            void* stream);
+
+/* dsa_indexer_topk for a rank of a head-sharded layer: the same call (same arguments, same results in
+ * `topk_out`, which here is the rank's slice -- rows [row_offset, row_offset + batch) -- of its
+ * [rows_total][topk_stride] index tensor), and in addition every finished row is stored as
+ * (id, epoch) pairs into row row_offset + b of every peer's staging buffer (`peer_stage`, `world`,
+ * `rank`, `epoch` as for dsa_index_rows_exchange; row width 2048).  On decode shapes the selection
+ * kernel sends each row itself as soon as it is complete, while other requests are still being
+ * selected; on the other shapes a push-only pass follows the selection.  Either way the caller
+ * then calls dsa_index_rows_exchange with mode = 2 (take) and the same epoch.  topk_stride even,
+ * topk_out 8-byte aligned. */
+int dsa_indexer_topk_send(const void* q_fp8, const void* k_cache, const float* weights,
+                          const int32_t* seq_lens, const int32_t* block_table,
+                          int64_t block_table_stride, int32_t* topk_out, int64_t topk_stride, int batch,
+                          int num_pages, int max_pages, void* workspace, size_t workspace_bytes,
+                          void* const* peer_stage, int world, int rank, int row_offset, uint32_t epoch,
+                          int32_t* status_dev, void* stream);
 
 /* Self-test of the bounded device-side waits (no counterpart in the reference, whose kernels spin
  * without a limit: sparse_fused.py:135-137).  One thread waits for at most `limit_ns` nanoseconds

@@ -144,7 +144,7 @@ def test_row_exchange_two_ranks_in_turn_on_one_gpu(cuda):
     def call(rank, epoch, limit_ns=2_000_000):
         offset = sum(counts[:rank])
         rc = lib.dsa_index_rows_exchange(rows[rank].data_ptr(), ctypes.addressof(stage_ptrs), 2, rank,
-                                         counts[rank], offset, total, width, width, epoch, limit_ns,
+                                         counts[rank], offset, total, width, width, epoch, 3, limit_ns,
                                          status.data_ptr(), workspace.stream_handle(cuda))
         _lib.check(rc, "dsa_index_rows_exchange")
 
@@ -166,11 +166,55 @@ def test_row_exchange_two_ranks_in_turn_on_one_gpu(cuda):
         assert torch.equal(rows[1], truth)
     # argument checks
     bad = lib.dsa_index_rows_exchange(rows[0].data_ptr(), ctypes.addressof(stage_ptrs), 9, 0, 1, 0, 8, width, width,
-                                      1, 1000, status.data_ptr(), None)
+                                      1, 3, 1000, status.data_ptr(), None)
     assert bad < 0
     bad = lib.dsa_index_rows_exchange(rows[0].data_ptr(), ctypes.addressof(stage_ptrs), 2, 0, 5, 0, 8, width, width,
-                                      0, 1000, status.data_ptr(), None)
+                                      0, 3, 1000, status.data_ptr(), None)
     assert bad < 0
+    bad = lib.dsa_index_rows_exchange(rows[0].data_ptr(), ctypes.addressof(stage_ptrs), 2, 0, 5, 0, 8, width, width,
+                                      1, 0, 1000, status.data_ptr(), None)
+    assert bad < 0
+
+
+@pytest.mark.parametrize("path", ["hist", "minmax"])
+def test_selection_sends_its_rows(cuda, monkeypatch, path):
+    """dsa_indexer_topk_send with the "peer" buffer on the same GPU: after the call the peer's staging
+    rows [offset, offset + B) hold (id, epoch) pairs of exactly the rows the indexer returned --
+    sent by the selection kernel itself on the histogram path (long and short rows, a row longer
+    than one CTA's slice), by the push-only pass on the other -- and nothing else was touched; the
+    take-only exchange on the "peer" then finds them."""
+    import ctypes
+    for p in (ROOT, ROOT / "oracle"):
+        if str(p) not in sys.path:
+            sys.path.insert(0, str(p))
+    from auto_gpu_kernel_b200 import _lib, indexer, inputs as wl, workspace
+    from helpers import assert_topk_matches
+    monkeypatch.setenv("DSA_INDEXER_PATH", path)
+    lens = [3000, 70, 2049, 50000, 2048, 9000]
+    inp = wl.make_indexer_inputs(lens, seed=31, device=cuda)
+    batch, offset, total, epoch = len(lens), 3, 12, 7
+    stage = [torch.zeros(total, 2048, 2, dtype=torch.int32, device=cuda) for _ in range(2)]
+    stage_ptrs = (ctypes.c_void_p * 2)(stage[0].data_ptr(), stage[1].data_ptr())
+    rows = torch.full((total, 2048), -9, dtype=torch.int32, device=cuda)     # rank 0's index tensor
+    indexer.kernel(*inp.args(), rows[offset:offset + batch],
+                   send=(ctypes.addressof(stage_ptrs), 2, 0, offset, epoch))
+    workspace.check_status(cuda)
+    assert_topk_matches(inp, rows[offset:offset + batch], label=f"{path}: local rows")
+    assert torch.equal(stage[1][offset:offset + batch, :, 0], rows[offset:offset + batch])
+    assert (stage[1][offset:offset + batch, :, 1] == epoch).all()
+    assert int(stage[1][:offset].abs().sum()) == 0 and int(stage[1][offset + batch:].abs().sum()) == 0
+    assert int(stage[0].abs().sum()) == 0                                   # nothing is sent to oneself
+    # the peer (rank 1, no rows of its own in this test) takes them
+    peer_rows = torch.full((total, 2048), -9, dtype=torch.int32, device=cuda)
+    lib = _lib.load()
+    rc = lib.dsa_index_rows_exchange(peer_rows.data_ptr(), ctypes.addressof(stage_ptrs), 2, 1, 0, total, total,
+                                     2048, 2048, epoch, 2, 2_000_000, workspace.status_word(cuda).data_ptr(),
+                                     workspace.stream_handle(cuda))
+    _lib.check(rc, "dsa_index_rows_exchange")
+    with pytest.raises(RuntimeError, match="0x1"):       # rows outside [offset, offset + B) never arrive
+        workspace.check_status(cuda)
+    assert torch.equal(peer_rows[offset:offset + batch], rows[offset:offset + batch])
+    assert (peer_rows[:offset] == -9).all() and (peer_rows[offset + batch:] == -9).all()
 
 
 def test_head_sharded_block_on_two_gpus(tmp_path):
