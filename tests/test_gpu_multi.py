@@ -112,6 +112,73 @@ def _push_worker(rank, world, port, result_path):
         dist.destroy_process_group()
 
 
+def _silent_peer_worker(rank, world, port, result_path):
+    """Rank 1 takes part in step 1 and then stays silent (alive, its buffers mapped, but it neither
+    selects nor sends); rank 0 runs step 2 alone with a poll limit of 50 ms.  Rank 0 must come back with
+    DSA_STATUS_WAIT_TIMEOUT, its own rows intact, and a usable context; nothing hangs or faults."""
+    for p in (ROOT, ROOT / "oracle"):
+        if str(p) not in sys.path:
+            sys.path.insert(0, str(p))
+    import time
+    import torch.distributed as dist
+    from auto_gpu_kernel_b200 import dist as dsa_dist, indexer, inputs as wl, workspace
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        lens = [3000, 2100, 5000, 2500]
+        counts = [2, 2]
+        sel = slice(2 * rank, 2 * rank + 2)
+        inp = wl.make_indexer_inputs(lens, seed=40, device=dev)
+        args = (inp.q_index_fp8[sel].contiguous(), inp.k_index_cache_fp8, inp.weights[sel].contiguous(),
+                inp.seq_lens[sel].contiguous(), inp.block_table[sel].contiguous())
+        plan = dsa_dist.PeerPushPlan(counts, rank, dev, wait_limit_ns=50_000_000)
+        want = indexer.run(*inp.args())
+        plan.run_indexer(*args)
+        rows = plan.gather().clone()
+        workspace.check_status(dev)
+        ok = torch.equal(torch.sort(rows, 1).values, torch.sort(want, 1).values)
+        dist.barrier()
+        verdict = "skipped"
+        if rank == 0:
+            t0 = time.perf_counter()
+            plan.run_indexer(*args)
+            plan.gather()
+            torch.cuda.synchronize(dev)
+            waited = time.perf_counter() - t0
+            try:
+                workspace.check_status(dev)
+                verdict = "no timeout was reported"
+            except RuntimeError as exc:
+                verdict = "ok" if "0x1" in str(exc) and 0.04 < waited < 5.0 else f"unexpected: {exc} after {waited:.3f} s"
+            mine = plan.all_rows[:2]
+            if not torch.equal(torch.sort(mine, 1).values, torch.sort(want[:2], 1).values):
+                verdict = "own rows damaged"
+            # the context is still good for ordinary work
+            again = indexer.run(*inp.args())
+            workspace.check_status(dev)
+            if not torch.equal(torch.sort(again, 1).values, torch.sort(want, 1).values):
+                verdict = "context unusable after the timeout"
+        dist.barrier()            # rank 1 has stayed alive (its buffers mapped) until rank 0 is done
+        plan.close()
+        if rank == 0:
+            Path(result_path).write_text(verdict if ok else "step 1 mismatch")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_silent_peer_ends_in_a_timeout_status(tmp_path):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    result = tmp_path / "result.txt"
+    mp.spawn(_silent_peer_worker, args=(2, _free_port(), str(result)), nprocs=2, join=True)
+    assert result.read_text() == "ok"
+
+
 def test_head_sharded_block_with_pushed_rows_on_two_gpus(tmp_path):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
