@@ -34,9 +34,6 @@ SIGNATURES = {
     "dsa_sparse_attn_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int]),
     "dsa_sparse_attn": (_c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _c_float, _ptr, _ptr,
                                  _c_int, _c_int, _c_int, _c_i64, _ptr, _c_size, _ptr, _ptr]),
-    "dsa_sparse_attn_take": (_c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _c_float, _ptr, _ptr,
-                                      _c_int, _c_int, _c_int, _c_i64, _ptr, _c_size, _ptr, _c_int, _c_int,
-                                      ctypes.c_uint32, ctypes.c_uint64, _ptr, _ptr]),
     "dsa_sparse_attn_tcgen05": (_c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _c_i64, _c_float, _ptr,
                                          _ptr, _c_int, _c_int, _c_int, _c_i64, _ptr, _c_size,
                                          _ptr, _ptr]),

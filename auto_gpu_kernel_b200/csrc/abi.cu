@@ -30,7 +30,7 @@ cudaError_t launch_index_rows_exchange(int32_t*, const RowSend&, int, int, int64
                                        cudaStream_t);
 cudaError_t launch_sparse_attn_mma(const void*, const void*, const void*, const void*,
                                    const int32_t*, int64_t, float, void*, float*, int, int, int64_t,
-                                   void*, const RowTake*, int32_t*, cudaStream_t);
+                                   void*, int32_t*, cudaStream_t);
 int att_pick_splits(int tokens, int topk);
 cudaError_t launch_indexer_score_prefill(const void*, const void*, const float*, const int32_t*,
                                          const int32_t*, float*, int64_t, int, int, int, int,
@@ -267,8 +267,7 @@ size_t dsa_sparse_attn_workspace_bytes(int tokens, int heads, int topk) {
 static int attn_impl(const void* q_nope, const void* q_pe, const void* ckv, const void* kpe,
                      const int32_t* sparse_indices, int64_t index_stride, float sm_scale, void* out,
                      float* lse, int tokens, int heads, int topk, int64_t num_slots, void* workspace,
-                     size_t workspace_bytes, int32_t* status_dev, void* stream, int variant,
-                     const dsa::RowTake* take = nullptr) {
+                     size_t workspace_bytes, int32_t* status_dev, void* stream, int variant) {
   if (tokens == 0) return DSA_OK;
   if (!q_nope || !q_pe || !ckv || !kpe || !sparse_indices || !out || !lse || !workspace)
     return DSA_ERR_NULL_POINTER;
@@ -294,7 +293,7 @@ static int attn_impl(const void* q_nope, const void* q_pe, const void* ckv, cons
   }
   return static_cast<int>(dsa::launch_sparse_attn_mma(q_nope, q_pe, ckv, kpe, sparse_indices,
                                                       index_stride, sm_scale, out, lse, tokens, topk,
-                                                      num_slots, workspace, take, status_dev, s));
+                                                      num_slots, workspace, status_dev, s));
 }
 
 int dsa_sparse_attn(const void* q_nope, const void* q_pe, const void* ckv, const void* kpe,
@@ -303,29 +302,6 @@ int dsa_sparse_attn(const void* q_nope, const void* q_pe, const void* ckv, const
                     size_t workspace_bytes, int32_t* status_dev, void* stream) {
   return attn_impl(q_nope, q_pe, ckv, kpe, sparse_indices, index_stride, sm_scale, out, lse, tokens,
                    heads, topk, num_slots, workspace, workspace_bytes, status_dev, stream, 0);
-}
-
-int dsa_sparse_attn_take(const void* q_nope, const void* q_pe, const void* ckv, const void* kpe,
-                         int32_t* sparse_indices, int64_t index_stride, float sm_scale, void* out,
-                         float* lse, int tokens, int heads, int topk, int64_t num_slots, void* workspace,
-                         size_t workspace_bytes, const void* own_stage, int row_offset, int rows_local,
-                         uint32_t epoch, uint64_t wait_limit_ns, int32_t* status_dev, void* stream) {
-  if (!own_stage || !sparse_indices) return DSA_ERR_NULL_POINTER;
-  if (row_offset < 0 || rows_local < 0 || row_offset + rows_local > tokens || epoch == 0 ||
-      topk % 2 != 0 || index_stride % 2 != 0 || wait_limit_ns == 0 || wait_limit_ns > 10000000000ull)
-    return DSA_ERR_BAD_SHAPE;
-  if (!aligned16(own_stage) || (reinterpret_cast<uintptr_t>(sparse_indices) & 7u)) return DSA_ERR_MISALIGNED;
-  dsa::RowTake tk = {};
-  tk.stage = static_cast<const uint2*>(own_stage);
-  tk.rows = sparse_indices;
-  tk.row_stride = index_stride;
-  tk.row_width = topk;
-  tk.row_offset = row_offset;
-  tk.rows_local = rows_local;
-  tk.epoch = epoch;
-  tk.limit_ns = wait_limit_ns;
-  return attn_impl(q_nope, q_pe, ckv, kpe, sparse_indices, index_stride, sm_scale, out, lse, tokens,
-                   heads, topk, num_slots, workspace, workspace_bytes, status_dev, stream, 0, &tk);
 }
 
 int dsa_sparse_attn_cuda_core(const void* q_nope, const void* q_pe, const void* ckv,

@@ -93,41 +93,6 @@ __device__ __forceinline__ uint2* own_stage(const RowSend& xs) {
   return p;
 }
 
-// The take side of the same exchange, for a kernel that consumes index rows: this rank's own
-// staging buffer, the index tensor the ids go to, which rows are the rank's own (never staged),
-// the epoch to wait for and the time limit of the poll.  stage == nullptr: rows are already there.
-struct RowTake {
-  const uint2* stage;
-  int32_t* rows;
-  int64_t row_stride;
-  int row_width, row_offset, rows_local;
-  uint32_t epoch;
-  unsigned long long limit_ns;
-};
-__device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-  return v;
-}
-// Two pairs (one 16-byte unit) of the staging buffer: poll until both carry `epoch`, within the time
-// limit; returns false when it ran out (`t0` keeps the start of the first wait of the calling thread).
-__device__ __forceinline__ bool take_unit(const uint4* src, uint32_t epoch, unsigned long long limit_ns,
-                                          unsigned long long& t0, int2& ids) {
-  uint4 v = ld_volatile_v4(src);
-  for (uint32_t spins = 0; v.y != epoch || v.w != epoch; ++spins) {
-    if ((spins & 31u) == 31u) {
-      unsigned long long now;
-      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > limit_ns) return false;
-    }
-    v = ld_volatile_v4(src);
-  }
-  ids = make_int2((int32_t)v.x, (int32_t)v.z);
-  return true;
-}
-
 // -inf and NaN scores are ranked as this value by the selection (and by the scorer's min / max).
 constexpr float kScoreFloor = -3.0e38f;
 

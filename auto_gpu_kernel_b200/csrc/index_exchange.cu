@@ -28,6 +28,13 @@ constexpr int kXchThreads = 256;
 
 namespace {
 
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
 __global__ void __launch_bounds__(kXchThreads)
 index_rows_exchange_kernel(int32_t* __restrict__ rows, const __grid_constant__ RowSend xs, int rows_local, int rows_total,
                            int64_t row_stride, int mode, uint64_t limit_ns, int32_t* status) {
@@ -51,12 +58,20 @@ index_rows_exchange_kernel(int32_t* __restrict__ rows, const __grid_constant__ R
     const int i = k < row_offset ? k : k + rows_local;
     int32_t* row = rows + (size_t)i * row_stride;
     const uint4* src = reinterpret_cast<const uint4*>(own_stage(xs) + (size_t)i * row_width);
-    unsigned long long t0 = 0;
+    uint64_t t0 = 0;
     bool gave_up = false;
-    for (int u = tid; u < pairs2 && !gave_up; u += kXchThreads) {
-      int2 ids;
-      if (take_unit(src + u, epoch, limit_ns, t0, ids)) reinterpret_cast<int2*>(row)[u] = ids;
-      else gave_up = true;
+    for (int u = tid; u < pairs2; u += kXchThreads) {
+      uint4 v = ld_volatile_v4(src + u);
+      for (uint32_t spins = 0; !gave_up && (v.y != epoch || v.w != epoch); ++spins) {
+        if ((spins & 31u) == 31u) {
+          const uint64_t now = ptx::global_timer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > limit_ns) gave_up = true;
+        }
+        v = ld_volatile_v4(src + u);
+      }
+      if (gave_up) break;
+      reinterpret_cast<int2*>(row)[u] = make_int2((int32_t)v.x, (int32_t)v.z);
     }
     if (gave_up) raise_status(status, DSA_STATUS_WAIT_TIMEOUT);
   }

@@ -153,14 +153,13 @@ __device__ __forceinline__ void mm_merge_segments(const AtPartials& part, long t
   }
 }
 
-template <bool kCluster, bool kTake>
+template <bool kCluster>
 __global__ void __launch_bounds__(kMmThreads, 1)
 sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bfloat16* __restrict__ q_pe,
                        const __nv_bfloat16* __restrict__ ckv, const __nv_bfloat16* __restrict__ kpe,
                        const int32_t* __restrict__ indices, int64_t index_stride, float scale_log2,
                        __nv_bfloat16* __restrict__ out, float* __restrict__ lse, int tokens, int topk,
-                       int64_t num_slots, AtPlan plan, void* ws_raw, const __grid_constant__ RowTake tk,
-                       int32_t* status) {
+                       int64_t num_slots, AtPlan plan, void* ws_raw, int32_t* status) {
   extern __shared__ unsigned char dyn_raw[];
   const uint32_t raw_addr = smem_u32(dyn_raw);
   const uint32_t pad = (128u - (raw_addr & 127u)) & 127u;
@@ -193,38 +192,14 @@ sparse_attn_mma_kernel(const __nv_bfloat16* __restrict__ q_nope, const __nv_bflo
   // indices of the next tile to issue (nv) and of the one after it (nw), two per lane: requested
   // two tiles ahead so that no issue ever waits for its index row (the first two go out together)
   int issued = 0, nv0 = -1, nv1 = -1, nw0 = -1, nw1 = -1;
-  constexpr bool taking = kTake;   // (then this CTA itself has just written the ids it reads)
   auto load_indices = [&](long tt, int jj, int& a, int& b) {
     const int k0 = jj * kAtTile + lane, k1 = k0 + 32;
-    const int32_t* p = indices + (size_t)tt * index_stride;
-    a = k0 < topk ? (taking ? __ldcg(p + k0) : __ldg(p + k0)) : -1;
-    b = k1 < topk ? (taking ? __ldcg(p + k1) : __ldg(p + k1)) : -1;
+    a = k0 < topk ? __ldg(indices + (size_t)tt * index_stride + k0) : -1;
+    b = k1 < topk ? __ldg(indices + (size_t)tt * index_stride + k1) : -1;
   };
   auto advance = [&]() { if (++ji == tpt) { ji = 0; ++ti; } };
   ptx::grid_dependency_wait();  // the index rows may come from the kernel before us in the stream
   ptx::launch_dependents();     // from here on the next kernel in the stream may run its set-up under our tail
-  if constexpr (kTake) {
-    // Head-sharded layer: the ids of other ranks' requests arrive as (id, epoch) pairs in this
-    // rank's staging buffer.  Every CTA takes the part of the rows that it is about to read -- its
-    // own tiles -- into the index tensor, polling with a time limit; a token's attention starts as
-    // soon as ITS row is there, whatever the other rows do.
-    unsigned long long t0 = 0;
-    bool gave_up = false;
-    for (int x = tid; x < n * (kAtTile / 2) && !gave_up; x += kMmThreads) {
-      const long wt = w0 + x / (kAtTile / 2);
-      const long tt = wt / tpt;
-      const int k0 = (int)(wt - tt * tpt) * kAtTile + 2 * (x % (kAtTile / 2));
-      if (k0 >= tk.row_width || (tt >= tk.row_offset && tt < tk.row_offset + tk.rows_local)) continue;
-      int2 ids;
-      if (take_unit(reinterpret_cast<const uint4*>(tk.stage + (size_t)tt * tk.row_width + k0), tk.epoch,
-                    tk.limit_ns, t0, ids))
-        *reinterpret_cast<int2*>(tk.rows + (size_t)tt * tk.row_stride + k0) = ids;
-      else
-        gave_up = true;
-    }
-    if (gave_up) raise_status(status, DSA_STATUS_WAIT_TIMEOUT);
-    __syncthreads();
-  }
   if (n > 0) { load_indices(ti, ji, nv0, nv1); advance(); }
   if (n > 1) { load_indices(ti, ji, nw0, nw1); advance(); }
   const int sub = lane >> 3, ch = lane & 7;  // row inside a 4-row group, 16-byte chunk of a 128-byte block
@@ -588,7 +563,7 @@ static int mm_max_active_clusters(int csize) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, sparse_attn_mma_kernel<true, false>, &cfg) != cudaSuccess || n <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&n, sparse_attn_mma_kernel<true>, &cfg) != cudaSuccess || n <= 0) {
       cudaGetLastError();
       n = -1;
     }
@@ -612,33 +587,23 @@ static int mm_cluster_size(int tokens, int tiles_per_token, int sms) {
 cudaError_t launch_sparse_attn_mma(const void* q_nope, const void* q_pe, const void* ckv,
                                    const void* kpe, const int32_t* indices, int64_t index_stride,
                                    float sm_scale, void* out, float* lse, int tokens, int topk,
-                                   int64_t num_slots, void* ws, const RowTake* take, int32_t* status,
-                                   cudaStream_t stream) {
-  RowTake tk = {};
-  if (take != nullptr) tk = *take;
-  const bool taking = tk.stage != nullptr;
-  static std::atomic<uint64_t> smem_opted[4] = {};
-  const void* kernels[4] = {reinterpret_cast<const void*>(sparse_attn_mma_kernel<false, false>),
-                            reinterpret_cast<const void*>(sparse_attn_mma_kernel<true, false>),
-                            reinterpret_cast<const void*>(sparse_attn_mma_kernel<false, true>),
-                            reinterpret_cast<const void*>(sparse_attn_mma_kernel<true, true>)};
+                                   int64_t num_slots, void* ws, int32_t* status, cudaStream_t stream) {
+  static std::atomic<uint64_t> smem_opted_a{0}, smem_opted_b{0};
+  {
+    cudaError_t e = opt_in_dynamic_smem(reinterpret_cast<const void*>(sparse_attn_mma_kernel<false>),
+                                        kMmDynBytes, smem_opted_a);
+    if (e == cudaSuccess)
+      e = opt_in_dynamic_smem(reinterpret_cast<const void*>(sparse_attn_mma_kernel<true>), kMmDynBytes,
+                              smem_opted_b);
+    if (e != cudaSuccess) return e;
+  }
   static int cluster_ok = -1;
   if (cluster_ok < 0) {   // DSA_ATT_CLUSTER=0 forces the contiguous-range split (for A/B timing)
     const char* e = getenv("DSA_ATT_CLUSTER");
     cluster_ok = (e != nullptr && e[0] == '0') ? 0 : 1;
   }
-  {
-    // (the cluster kernel first: the occupancy query inside mm_cluster_size needs its opt-in)
-    cudaError_t e = opt_in_dynamic_smem(kernels[1], kMmDynBytes, smem_opted[1]);
-    if (e != cudaSuccess) return e;
-  }
   AtPlan plan = at_make_plan(tokens, topk, sm_count());
   const int csize = cluster_ok ? mm_cluster_size(tokens, plan.tiles_per_token, sm_count()) : 0;
-  const int which = (csize > 0 ? 1 : 0) + (taking ? 2 : 0);
-  if (which != 1) {
-    cudaError_t e = opt_in_dynamic_smem(kernels[which], kMmDynBytes, smem_opted[which]);
-    if (e != cudaSuccess) return e;
-  }
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kMmThreads);
   cfg.dynamicSmemBytes = kMmDynBytes;
@@ -656,22 +621,22 @@ cudaError_t launch_sparse_attn_mma(const void* q_nope, const void* q_pe, const v
     attr[1].val.clusterDim.y = 1;
     attr[1].val.clusterDim.z = 1;
     cfg.numAttrs = 2;
-  } else {
-    cfg.gridDim = dim3((unsigned)plan.grid);
-  }
-  auto launch = [&](auto kernel) {
-    return cudaLaunchKernelEx(&cfg, kernel, static_cast<const __nv_bfloat16*>(q_nope),
-                              static_cast<const __nv_bfloat16*>(q_pe), static_cast<const __nv_bfloat16*>(ckv),
+    return cudaLaunchKernelEx(&cfg, sparse_attn_mma_kernel<true>,
+                              static_cast<const __nv_bfloat16*>(q_nope),
+                              static_cast<const __nv_bfloat16*>(q_pe),
+                              static_cast<const __nv_bfloat16*>(ckv),
                               static_cast<const __nv_bfloat16*>(kpe), indices, index_stride,
                               sm_scale * kMmLog2e, static_cast<__nv_bfloat16*>(out), lse, tokens, topk,
-                              num_slots, plan, ws, tk, status);
-  };
-  switch (which) {
-    case 0: return launch(sparse_attn_mma_kernel<false, false>);
-    case 1: return launch(sparse_attn_mma_kernel<true, false>);
-    case 2: return launch(sparse_attn_mma_kernel<false, true>);
-    default: return launch(sparse_attn_mma_kernel<true, true>);
+                              num_slots, plan, ws, status);
   }
+  cfg.gridDim = dim3((unsigned)plan.grid);
+  return cudaLaunchKernelEx(&cfg, sparse_attn_mma_kernel<false>,
+                            static_cast<const __nv_bfloat16*>(q_nope),
+                            static_cast<const __nv_bfloat16*>(q_pe),
+                            static_cast<const __nv_bfloat16*>(ckv),
+                            static_cast<const __nv_bfloat16*>(kpe), indices, index_stride,
+                            sm_scale * kMmLog2e, static_cast<__nv_bfloat16*>(out), lse, tokens, topk,
+                            num_slots, plan, ws, status);
 }
 
 }  // namespace dsa

@@ -243,20 +243,6 @@ class PeerPushPlan:
         if send is not None:
             self._sent = nxt
 
-    def take_in_attention(self):
-        """Instead of `gather()`: advance to the step whose rows `run_indexer` has just sent and
-        return the `take=` argument for `sparse_attention.kernel`, which then takes the peers' rows
-        itself, each CTA the ids it is about to read (no exchange kernel at all).  Returns None when
-        there is nothing to take (one rank) -- or raises if the rows were not sent by `run_indexer`."""
-        if self.world == 1:
-            self.epoch += 1
-            return None
-        if self._sent != self.epoch + 1:
-            raise RuntimeError("take_in_attention: call run_indexer first (it sends the rows)")
-        self.epoch += 1
-        own = self._stage_ptrs[self.epoch & 1][self.rank]
-        return (own, self.offset, self.counts[self.rank], self._epoch_word(self.epoch), self.wait_limit_ns)
-
     def gather(self):
         self.epoch += 1
         mode = 2 if self._sent == self.epoch else 3
@@ -302,7 +288,6 @@ def decode_block_head_sharded(idx_args_local, counts, q_nope_heads, q_pe_heads, 
     """
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     fused = indexer_fn is None and hasattr(plan, "run_indexer")
-    fused_attention = attention_fn is None and hasattr(plan, "take_in_attention")
     if indexer_fn is None or attention_fn is None:
         default_indexer, default_attention = _default_ops()
         indexer_fn = indexer_fn or default_indexer
@@ -313,17 +298,10 @@ def decode_block_head_sharded(idx_args_local, counts, q_nope_heads, q_pe_heads, 
         plan.run_indexer(*idx_args_local)      # the selection kernel sends the rows itself
     else:
         indexer_fn(*idx_args_local, plan.local_rows)
-    if fused and fused_attention and plan.width % 64 == 0:
-        # ... and the attention kernel takes the peers' rows itself: no exchange kernel at all
-        take = plan.take_in_attention()
-        all_indices = plan.all_rows
-        attention_fn(q_nope_heads, q_pe_heads, ckv_cache, kpe_cache, all_indices, sm_scale, output, lse,
-                     take=take)
-    else:
-        all_indices = plan.gather()
-        attention_fn(q_nope_heads, q_pe_heads, ckv_cache, kpe_cache, all_indices, sm_scale, output, lse)
+    all_indices = plan.gather()
     if local_indices is not None:
         local_indices.copy_(plan.local_rows)
+    attention_fn(q_nope_heads, q_pe_heads, ckv_cache, kpe_cache, all_indices, sm_scale, output, lse)
     return all_indices
 
 

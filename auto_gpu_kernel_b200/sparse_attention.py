@@ -18,14 +18,10 @@ CKV = 512
 KPE = 64
 
 
-def kernel(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale, output, lse, variant=0, take=None):
+def kernel(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale, output, lse, variant=0):
     """Write attention output and base-2 LSE in place; enqueued on the current stream, returns None.
     `variant` 0 = default (warp-level mma.sync) kernel, 1 = CUDA-core cross-check kernel, 2 =
-    tcgen05/TMEM kernel (not part of the reference signature; positional callers never pass it).
-
-    `take` (head-sharded layers only, see `dist.PeerPushPlan`): (address of this rank's staging
-    buffer, row_offset, rows_local, epoch, wait limit in ns) -- the kernel first takes the other
-    ranks' index rows out of the staging buffer into `sparse_indices` (`dsa_sparse_attn_take`)."""
+    tcgen05/TMEM kernel (not part of the reference signature; positional callers never pass it)."""
     if not q_nope.is_cuda:
         raise RuntimeError("dsa sparse attention: CUDA tensors required (this operator has no CPU path)")
     dev = q_nope.device
@@ -62,24 +58,13 @@ def kernel(q_nope, q_pe, ckv_cache, kpe_cache, sparse_indices, sm_scale, output,
     need = lib.dsa_sparse_attn_workspace_bytes(tokens, HEADS, topk)
     ws = workspace.get(dev, "attention", need)
     with workspace.device_guard(dev):
-        if take is not None:
-            if variant != 0:
-                raise ValueError("take= is a feature of the default attention kernel")
-            stage, row_offset, rows_local, epoch, limit_ns = take
-            rc = lib.dsa_sparse_attn_take(
-                q_nope.data_ptr(), q_pe.data_ptr(), ckv_cache.data_ptr(), kpe_cache.data_ptr(),
-                sparse_indices.data_ptr(), sparse_indices.stride(0), float(sm_scale),
-                output.data_ptr(), lse.data_ptr(), tokens, HEADS, topk, slots, ws.data_ptr(),
-                ws.numel(), stage, row_offset, rows_local, epoch, limit_ns,
-                workspace.status_word(dev).data_ptr(), workspace.stream_handle(dev))
-        else:
-            fn = (lib.dsa_sparse_attn, lib.dsa_sparse_attn_cuda_core, lib.dsa_sparse_attn_tcgen05)[variant]
-            rc = fn(
-                q_nope.data_ptr(), q_pe.data_ptr(), ckv_cache.data_ptr(), kpe_cache.data_ptr(),
-                sparse_indices.data_ptr(), sparse_indices.stride(0), float(sm_scale),
-                output.data_ptr(), lse.data_ptr(), tokens, HEADS, topk, slots, ws.data_ptr(),
-                ws.numel(), workspace.status_word(dev).data_ptr(),
-                workspace.stream_handle(dev))
+        fn = (lib.dsa_sparse_attn, lib.dsa_sparse_attn_cuda_core, lib.dsa_sparse_attn_tcgen05)[variant]
+        rc = fn(
+            q_nope.data_ptr(), q_pe.data_ptr(), ckv_cache.data_ptr(), kpe_cache.data_ptr(),
+            sparse_indices.data_ptr(), sparse_indices.stride(0), float(sm_scale),
+            output.data_ptr(), lse.data_ptr(), tokens, HEADS, topk, slots, ws.data_ptr(),
+            ws.numel(), workspace.status_word(dev).data_ptr(),
+            workspace.stream_handle(dev))
     _lib.check(rc, "dsa_sparse_attn")
     return None
 

@@ -296,20 +296,6 @@ int dsa_indexer_topk_send(const void* q_fp8, const void* k_cache, const float* w
                           void* const* peer_stage, int world, int rank, int row_offset, uint32_t epoch,
                           int32_t* status_dev, void* stream);
 
-/* dsa_sparse_attn for a rank of a head-sharded layer, with the take side of the row exchange inside
- * the attention kernel: `sparse_indices` is the rank's own [tokens][index_stride] index tensor, of
- * which only the rows [row_offset, row_offset + rows_local) are valid on entry; every CTA first takes
- * the ids it is about to read out of `own_stage` (this rank's staging buffer of (id, epoch) pairs, row
- * width `topk`) into the tensor, polling until they carry `epoch` (time limit, status and alignment
- * rules as for dsa_index_rows_exchange), so that a token's attention starts as soon as its own row
- * has arrived.  Replaces dsa_index_rows_exchange(mode = 2) + dsa_sparse_attn; afterwards
- * `sparse_indices` holds every row that some CTA has read (all of them when topk is a multiple of 64). */
-int dsa_sparse_attn_take(const void* q_nope, const void* q_pe, const void* ckv, const void* kpe,
-                         int32_t* sparse_indices, int64_t index_stride, float sm_scale, void* out,
-                         float* lse, int tokens, int heads, int topk, int64_t num_slots, void* workspace,
-                         size_t workspace_bytes, const void* own_stage, int row_offset, int rows_local,
-                         uint32_t epoch, uint64_t wait_limit_ns, int32_t* status_dev, void* stream);
-
 /* Self-test of the bounded device-side waits (no counterpart in the reference, whose kernels spin
  * without a limit: sparse_fused.py:135-137).  One thread waits for at most `limit_ns` nanoseconds
  * (1 .. 1e9) on a barrier that receives no arrival, then sets DSA_STATUS_WAIT_TIMEOUT in

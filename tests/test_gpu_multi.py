@@ -112,40 +112,6 @@ def _push_worker(rank, world, port, result_path):
         dist.destroy_process_group()
 
 
-def test_attention_takes_the_rows_itself(cuda):
-    """dsa_sparse_attn_take with the sender on the same GPU: rank 0's indexer sends all its rows to
-    "rank 1", whose attention -- no rows of its own, an index tensor full of junk -- takes them out
-    of its staging buffer inside the kernel.  Output and LSE equal the plain attention over rank 0's
-    rows bit for bit, and the index tensor ends up equal to them.  With a wrong epoch the poll runs
-    out (2 ms) and the call reports DSA_STATUS_WAIT_TIMEOUT."""
-    import ctypes
-    for p in (ROOT, ROOT / "oracle"):
-        if str(p) not in sys.path:
-            sys.path.insert(0, str(p))
-    from auto_gpu_kernel_b200 import indexer, inputs as wl, sparse_attention, workspace
-    for lens in ([3000, 70, 2049, 9000, 5000], [4000] * 70):      # cluster split and contiguous split
-        blk = wl.make_decode_block_inputs(lens, seed=41, device=cuda)
-        batch, epoch = len(lens), 3
-        stage = [torch.zeros(batch, 2048, 2, dtype=torch.int32, device=cuda) for _ in range(2)]
-        stage_ptrs = (ctypes.c_void_p * 2)(stage[0].data_ptr(), stage[1].data_ptr())
-        rows0 = torch.empty(batch, 2048, dtype=torch.int32, device=cuda)
-        indexer.kernel(*blk.indexer.args(), rows0, send=(ctypes.addressof(stage_ptrs), 2, 0, 0, epoch))
-        want_out, want_lse = sparse_attention.run(blk.q_nope, blk.q_pe, blk.ckv_cache, blk.kpe_cache, rows0,
-                                                  blk.sm_scale)
-        rows1 = torch.full((batch, 2048), 5, dtype=torch.int32, device=cuda)
-        out = torch.empty_like(want_out)
-        lse = torch.empty_like(want_lse)
-        sparse_attention.kernel(blk.q_nope, blk.q_pe, blk.ckv_cache, blk.kpe_cache, rows1, blk.sm_scale, out, lse,
-                                take=(stage[1].data_ptr(), 0, 0, epoch, 2_000_000))
-        assert workspace.check_status(cuda) == 0
-        assert torch.equal(rows1, rows0)
-        assert torch.equal(out.view(torch.int16), want_out.view(torch.int16)) and torch.equal(lse, want_lse)
-        sparse_attention.kernel(blk.q_nope, blk.q_pe, blk.ckv_cache, blk.kpe_cache, rows1, blk.sm_scale, out, lse,
-                                take=(stage[1].data_ptr(), 0, 0, epoch + 1, 2_000_000))
-        with pytest.raises(RuntimeError, match="0x1"):
-            workspace.check_status(cuda)
-
-
 def _silent_peer_worker(rank, world, port, result_path):
     """Rank 1 takes part in step 1 and then stays silent (alive, its buffers mapped, but it neither
     selects nor sends); rank 0 runs step 2 alone with a poll limit of 50 ms.  Rank 0 must come back with
