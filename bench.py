@@ -166,14 +166,22 @@ def ev():
 
 
 def timed_us(step, steps, warmup, ranks, sampler=None):
-    """Mean microseconds per step: W warm-ups, then exactly K steps between two events."""
+    """Mean microseconds per step: W warm-ups, then exactly K steps between two events.
+
+    The K steps of a decode workload last a millisecond or two, so a host hiccup (another rank's
+    process start, the clock sampler's) would otherwise show up as device time.  Two precautions:
+    the sampler is started -- and given time to come up -- before the warm-up, and the first event
+    is recorded behind a short device-side delay, during which the host has already queued the K
+    steps: the device then runs them back to back, as a serving loop that runs ahead of the GPU does."""
+    if sampler is not None:
+        sampler.start()
+        time.sleep(0.4)
     for _ in range(max(warmup, 3)):
         step()
     ranks.barrier()
-    if sampler is not None:
-        sampler.start()
     e0, e1 = ev(), ev()
     ranks.barrier()
+    torch.cuda._sleep(int(min(4.0e-3, max(1.0e-3, steps * 6.0e-5)) * 1.9e9))   # 1-4 ms of device time
     e0.record()
     for _ in range(steps):
         step()
