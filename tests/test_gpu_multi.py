@@ -142,7 +142,7 @@ def _silent_peer_worker(rank, world, port, result_path):
         workspace.check_status(dev)
         ok = torch.equal(torch.sort(rows, 1).values, torch.sort(want, 1).values)
         dist.barrier()
-        verdict = "skipped"
+        outcome = "skipped"
         if rank == 0:
             t0 = time.perf_counter()
             plan.run_indexer(*args)
@@ -151,21 +151,21 @@ def _silent_peer_worker(rank, world, port, result_path):
             waited = time.perf_counter() - t0
             try:
                 workspace.check_status(dev)
-                verdict = "no timeout was reported"
+                outcome = "no timeout was reported"
             except RuntimeError as exc:
-                verdict = "ok" if "0x1" in str(exc) and 0.04 < waited < 5.0 else f"unexpected: {exc} after {waited:.3f} s"
+                outcome = "ok" if "0x1" in str(exc) and 0.04 < waited < 5.0 else f"unexpected: {exc} after {waited:.3f} s"
             mine = plan.all_rows[:2]
             if not torch.equal(torch.sort(mine, 1).values, torch.sort(want[:2], 1).values):
-                verdict = "own rows damaged"
+                outcome = "own rows damaged"
             # the context is still good for ordinary work
             again = indexer.run(*inp.args())
             workspace.check_status(dev)
             if not torch.equal(torch.sort(again, 1).values, torch.sort(want, 1).values):
-                verdict = "context unusable after the timeout"
+                outcome = "context unusable after the timeout"
         dist.barrier()            # rank 1 has stayed alive (its buffers mapped) until rank 0 is done
         plan.close()
         if rank == 0:
-            Path(result_path).write_text(verdict if ok else "step 1 mismatch")
+            Path(result_path).write_text(outcome if ok else "step 1 mismatch")
     finally:
         dist.destroy_process_group()
 
